@@ -1,0 +1,25 @@
+"""B200-native backend for the dense data-parallel array path of AMDGPU.jl.
+
+Host-side mirror of the reference's operator surface for that path (``ROCArray``, fused
+broadcast, ``mapreducedim!`` and the reductions on it, ``accumulate!``/``cumsum``,
+``sort!``/``sortperm``, the memory pool and the stream runtime) over the C ABI declared in
+``include/b200arrays.h``.  The kernels live in ``lib/libb200arrays.so``; importing this
+package fails loudly when that library is missing - there is no CPU fallback.
+"""
+from . import _lib
+from ._lib import B200Error, OutOfMemoryError
+from .runtime import (Stream, Event, elapsed_ms, elapsed, ndevices, devices, current_device, device_,
+                      current_stream, stream_, using_stream, priority_, synchronize, device_synchronize,
+                      device_properties, can_access_peer, versioninfo, functional)
+from .memory import (mem_info, parse_memory_limit, configure, reclaim, reclaim_hook, pool_alloc, pool_free,
+                     pool_stats, used_memory, cached_memory)
+from .array import ROCArray, copyto_, zeros, ones, fill, roc
+from . import broadcast
+from .broadcast import Broadcasted, materialize_, promote_type
+from .mapreduce import mapreducedim_, mapreduce, sum, prod, maximum, minimum   # noqa: A004
+from .accumulate import accumulate_, accumulate, cumsum, cumprod
+from .sorting import sort_, sort, sortperm_, sortperm
+from . import random
+from . import sharded
+
+__all__ = [n for n in dir() if not n.startswith("_")]

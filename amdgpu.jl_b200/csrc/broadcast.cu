@@ -1,0 +1,406 @@
+// Fused elementwise broadcast: out[I] = program(leaves[I]...).
+//
+// Takes the place of the kernel GPUArrays generates for a Broadcasted{ROCArrayStyle} tree
+// (style selection in src/broadcast.jl:3-30 of the reference).  Instead of JIT-compiling one
+// kernel per expression type, the tree arrives as a postfix program over a fixed operator set
+// and is either matched against hard-wired streaming kernels (a*x+y, x*y+exp(-|z|)) or run by
+// the register-stack evaluator of program.cuh.  Every path streams each operand exactly once
+// with 128-bit accesses: the algorithmic traffic is sizeof(T) per array leaf plus sizeof(T)
+// for the destination, per element.
+#include "program.cuh"
+
+#include <cstring>
+#include <vector>
+
+namespace b200 {
+
+// ---- host: scalar conversions -------------------------------------------------------------------
+static float half_bits_to_float(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000) << 16;
+    uint32_t exp = (h >> 10) & 0x1f;
+    uint32_t man = h & 0x3ff;
+    uint32_t f;
+    if (exp == 0) {
+        if (man == 0) f = sign;
+        else {
+            int e = -1;
+            do { man <<= 1; ++e; } while (!(man & 0x400));
+            f = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ff) << 13);
+        }
+    } else if (exp == 31) f = sign | 0x7f800000u | (man << 13);
+    else f = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    float out;
+    memcpy(&out, &f, 4);
+    return out;
+}
+
+uint64_t scalar_to_class(int32_t dt, uint64_t bits) {
+    switch (dt) {
+        case B200_F16: { float f = half_bits_to_float((uint16_t)bits); uint32_t u; memcpy(&u, &f, 4); return u; }
+        case B200_BF16: return (uint64_t)((uint32_t)(bits & 0xffff) << 16);
+        case B200_I8: return (uint32_t)(int32_t)(int8_t)bits;
+        case B200_I16: return (uint32_t)(int32_t)(int16_t)bits;
+        case B200_U8: case B200_BOOL: return bits & 0xff;
+        case B200_U16: return bits & 0xffff;
+        case B200_F32: case B200_I32: case B200_U32: return bits & 0xffffffffu;
+        default: return bits;
+    }
+}
+
+// ---- host: program validation ---------------------------------------------------------------------
+int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* leaves, int32_t nleaves,
+                        const uint8_t* program, int32_t ninstr, int32_t final_dtype, Compiled* out) {
+    if (ndim < 0 || ndim > B200_MAX_DIMS) return fail(B200_INVALID_ARG, "program: ndim %d outside [0,%d]", ndim, B200_MAX_DIMS);
+    if (nleaves < 0 || nleaves > B200_MAX_LEAVES) return fail(B200_INVALID_ARG, "program: %d leaves (at most %d)", nleaves, B200_MAX_LEAVES);
+    if (ninstr <= 0 || ninstr > B200_MAX_PROGRAM) return fail(B200_INVALID_ARG, "program: %d instructions (1..%d)", ninstr, B200_MAX_PROGRAM);
+    if (!program || (nleaves > 0 && !leaves)) return fail(B200_INVALID_ARG, "program: null pointer");
+    memset(out, 0, sizeof *out);
+    ProgramDesc& P = out->P;
+    P.ndim = ndim;
+    P.nleaves = nleaves;
+    int64_t numel = 1;
+    for (int d = 0; d < ndim; ++d) { P.shape[d] = shape[d]; numel *= shape[d]; }
+    bool linear = true, vec_ok = true;
+    bool wide = false;
+    for (int k = 0; k < nleaves; ++k) {
+        const b200_leaf& lf = leaves[k];
+        LeafDesc& L = P.leaves[k];
+        if (dtype_size(lf.t.dtype) == 0) return fail(B200_UNSUPPORTED, "leaf %d: unknown dtype %d", k, lf.t.dtype);
+        L.dtype = lf.t.dtype;
+        L.is_scalar = lf.is_scalar ? 1 : 0;
+        if (dtype_class(L.dtype) == CF64 || dtype_class(L.dtype) == CI64 || dtype_class(L.dtype) == CU64) wide = true;
+        if (lf.is_scalar) {
+            L.scalar = scalar_to_class(L.dtype, lf.scalar);
+            continue;
+        }
+        B200_TRY(check_tensor(&lf.t, "broadcast leaf"));
+        if (lf.t.ndim > ndim) return fail(B200_INVALID_ARG, "leaf %d has %d dims, index space has %d", k, lf.t.ndim, ndim);
+        L.ptr = lf.t.ptr;
+        int64_t expect = 1;
+        bool dense = true;
+        for (int d = 0; d < ndim; ++d) {
+            int64_t e = d < lf.t.ndim ? lf.t.shape[d] : 1;
+            int64_t s = d < lf.t.ndim ? lf.t.stride[d] : 0;
+            if (e != shape[d] && e != 1) return fail(B200_INVALID_ARG, "leaf %d: extent %lld in dim %d does not broadcast to %lld", k, (long long)e, d, (long long)shape[d]);
+            if (e == 1) s = 0;
+            L.stride[d] = s;
+            if (shape[d] != 1) { if (s != expect) dense = false; }
+            expect *= shape[d];
+        }
+        out->n_array_leaves++;
+        if (!dense) linear = false;
+        if (reinterpret_cast<uintptr_t>(L.ptr) % (dtype_size(L.dtype) * kVec) != 0) vec_ok = false;
+    }
+    // abstract interpretation: stack of dtypes
+    int32_t stack[kMaxStack + 1];
+    int sp = 0;
+    int nout = 0;
+    auto emit = [&](int op, int arg) { P.code[2 * nout] = (uint8_t)op; P.code[2 * nout + 1] = (uint8_t)arg; ++nout; };
+    for (int pc = 0; pc < ninstr; ++pc) {
+        const int op = program[2 * pc], arg = program[2 * pc + 1];
+        switch (op) {
+            case B200_OP_LEAF:
+                if (arg >= nleaves) return fail(B200_INVALID_ARG, "instruction %d: leaf %d does not exist", pc, arg);
+                if (sp >= kMaxStack) return fail(B200_UNSUPPORTED, "program needs a value stack deeper than %d", kMaxStack);
+                stack[sp++] = P.leaves[arg].dtype;
+                emit(op, arg);
+                break;
+            case B200_OP_CONVERT: {
+                if (sp < 1) return fail(B200_INVALID_ARG, "instruction %d: empty stack", pc);
+                if (arg >= B200_DTYPE_COUNT) return fail(B200_UNSUPPORTED, "instruction %d: unknown dtype %d", pc, arg);
+                const int src = stack[sp - 1];
+                if (src != arg) emit(op, (src << 4) | arg);
+                stack[sp - 1] = arg;
+                break;
+            }
+            case B200_OP_ABS: case B200_OP_ABS2: case B200_OP_EXP: case B200_OP_NEG:
+                if (sp < 1) return fail(B200_INVALID_ARG, "instruction %d: empty stack", pc);
+                if (stack[sp - 1] != arg) return fail(B200_INVALID_ARG, "instruction %d: operand dtype %d differs from the instruction's %d", pc, stack[sp - 1], arg);
+                if (op == B200_OP_EXP && !dtype_is_float(arg)) return fail(B200_UNSUPPORTED, "exp needs a floating-point operand");
+                if (arg == B200_BOOL) return fail(B200_UNSUPPORTED, "arithmetic on Bool values must be converted first");
+                emit(op, arg);
+                break;
+            case B200_OP_ADD: case B200_OP_SUB: case B200_OP_MUL: case B200_OP_DIV:
+            case B200_OP_MAX: case B200_OP_MIN:
+                if (sp < 2) return fail(B200_INVALID_ARG, "instruction %d: needs two operands", pc);
+                if (stack[sp - 1] != arg || stack[sp - 2] != arg) return fail(B200_INVALID_ARG, "instruction %d: operand dtypes (%d,%d) differ from the instruction's %d", pc, stack[sp - 2], stack[sp - 1], arg);
+                if (op == B200_OP_DIV && !dtype_is_float(arg)) return fail(B200_UNSUPPORTED, "/ needs floating-point operands (Base converts integers first)");
+                if (arg == B200_BOOL) return fail(B200_UNSUPPORTED, "arithmetic on Bool values must be converted first");
+                --sp;
+                emit(op, arg);
+                break;
+            case B200_OP_MULADD:
+                if (sp < 3) return fail(B200_INVALID_ARG, "instruction %d: needs three operands", pc);
+                if (stack[sp - 1] != arg || stack[sp - 2] != arg || stack[sp - 3] != arg) return fail(B200_INVALID_ARG, "instruction %d: operand dtypes differ from the instruction's %d", pc, arg);
+                if (arg == B200_BOOL) return fail(B200_UNSUPPORTED, "arithmetic on Bool values must be converted first");
+                sp -= 2;
+                emit(op, arg);
+                break;
+            default:
+                return fail(B200_UNSUPPORTED, "instruction %d: unknown opcode %d", pc, op);
+        }
+        if (op != B200_OP_LEAF && arg < B200_DTYPE_COUNT) {
+            int c = dtype_class(op == B200_OP_CONVERT ? arg : stack[sp - 1]);
+            if (c == CF64 || c == CI64 || c == CU64) wide = true;
+        }
+    }
+    if (sp != 1) return fail(B200_INVALID_ARG, "program leaves %d values on the stack (expected 1)", sp);
+    if (final_dtype >= 0 && stack[0] != final_dtype) {
+        if (final_dtype >= B200_DTYPE_COUNT) return fail(B200_UNSUPPORTED, "unknown result dtype %d", final_dtype);
+        emit(B200_OP_CONVERT, (stack[0] << 4) | final_dtype);
+        int c = dtype_class(final_dtype);
+        if (c == CF64 || c == CI64 || c == CU64) wide = true;
+        stack[0] = final_dtype;
+    }
+    P.ninstr = nout;
+    P.linear = linear ? 1 : 0;
+    P.vec_ok = (linear && vec_ok) ? 1 : 0;
+    out->result_dtype = stack[0];
+    out->wide = wide;
+    (void)numel;
+    return B200_OK;
+}
+
+// ---- device: evaluator kernel -------------------------------------------------------------------------
+template <bool WIDE>
+__global__ void __launch_bounds__(256)
+ew_program_kernel(const __grid_constant__ ProgramDesc P, const __grid_constant__ LeafDesc O, int64_t n) {
+    using R = typename RawOf<WIDE>::type;
+    const int64_t nvec = (n + kVec - 1) / kVec;
+    const bool out_linear = P.linear != 0;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+        int64_t lin[kVec];
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) lin[j] = v * kVec + j;
+        const int64_t left = n - v * kVec;
+        const int nvalid = left < kVec ? (int)left : kVec;
+        R res[kVec];
+        eval_program<WIDE>(P, lin, nvalid, res);
+        if (out_linear) {
+            store_vec4<R>(const_cast<void*>(O.ptr), O.dtype, lin[0], P.vec_ok != 0, nvalid, res);
+        } else {
+            const int bytes = dtype_bytes(O.dtype);
+#pragma unroll
+            for (int j = 0; j < kVec; ++j)
+                if (j < nvalid) store_bits(const_cast<void*>(O.ptr), bytes, leaf_offset(P, O, lin[j]), encode<R>(O.dtype, res[j]));
+        }
+    }
+}
+
+// ---- device: hard-wired streaming kernels --------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    using C = float;
+    static __device__ __forceinline__ float up(float v) { return v; }
+    static __device__ __forceinline__ float down(float v) { return v; }
+    static __device__ __forceinline__ float rnd(float v) { return v; }
+};
+template <> struct Elem<double> {
+    using C = double;
+    static __device__ __forceinline__ double up(double v) { return v; }
+    static __device__ __forceinline__ double down(double v) { return v; }
+    static __device__ __forceinline__ double rnd(double v) { return v; }
+};
+template <> struct Elem<__half> {
+    using C = float;
+    static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ float rnd(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    using C = float;
+    static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+// z = a*x + y, multiply and add rounded separately (Base does not contract `a .* x .+ y`).
+template <typename T>
+struct AxpyF {
+    typename Elem<T>::C a;
+    __device__ __forceinline__ T operator()(T x, T y, T) const {
+        using E = Elem<T>;
+        using A = Arith<typename E::C>;
+        typename E::C p = E::rnd(A::mul(a, E::up(x)));
+        return E::down(A::add(p, E::up(y)));
+    }
+};
+// r = x*y + exp(-abs(z))
+template <typename T>
+struct MulAddExpNegAbsF {
+    __device__ __forceinline__ T operator()(T x, T y, T z) const {
+        using E = Elem<T>;
+        using A = Arith<typename E::C>;
+        typename E::C p = E::rnd(A::mul(E::up(x), E::up(y)));
+        typename E::C e = E::rnd(A::exp(A::neg(A::abs(E::up(z)))));
+        return E::down(A::add(p, e));
+    }
+};
+
+constexpr int kEwThreads = 256;
+constexpr int kEwUnroll = 4;
+
+template <typename T, typename F, int NIN>
+__global__ void __launch_bounds__(kEwThreads)
+ew_stream_kernel(T* out, const T* in0, const T* in1, const T* in2, F f, int64_t n, int vec_ok) {
+    constexpr int V = 16 / sizeof(T);
+    constexpr int64_t TILE = (int64_t)kEwThreads * kEwUnroll * V;
+    const int64_t ntiles = (n + TILE - 1) / TILE;
+    using VT = Vec<T, V>;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t base = tile * TILE;
+        if (vec_ok && base + TILE <= n) {
+            VT a[kEwUnroll], b[kEwUnroll], c[kEwUnroll];
+#pragma unroll
+            for (int u = 0; u < kEwUnroll; ++u) {
+                const int64_t vi = base / V + (int64_t)u * kEwThreads + threadIdx.x;
+                a[u] = __builtin_bit_cast(VT, __ldcs(reinterpret_cast<const uint4*>(in0) + vi));
+                if (NIN > 1) b[u] = __builtin_bit_cast(VT, __ldcs(reinterpret_cast<const uint4*>(in1) + vi));
+                if (NIN > 2) c[u] = __builtin_bit_cast(VT, __ldcs(reinterpret_cast<const uint4*>(in2) + vi));
+            }
+#pragma unroll
+            for (int u = 0; u < kEwUnroll; ++u) {
+                const int64_t vi = base / V + (int64_t)u * kEwThreads + threadIdx.x;
+                VT r;
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    r.v[k] = f(a[u].v[k], NIN > 1 ? b[u].v[k] : a[u].v[k], NIN > 2 ? c[u].v[k] : a[u].v[k]);
+                __stcs(reinterpret_cast<uint4*>(out) + vi, __builtin_bit_cast(uint4, r));
+            }
+        } else {
+            const int64_t end = base + TILE < n ? base + TILE : n;
+            for (int64_t i = base + threadIdx.x; i < end; i += kEwThreads) {
+                T x = in0[i];
+                T y = NIN > 1 ? in1[i] : x;
+                T z = NIN > 2 ? in2[i] : x;
+                out[i] = f(x, y, z);
+            }
+        }
+    }
+}
+
+template <typename T, typename F, int NIN>
+static void launch_stream(b200_stream_t st, void* out, const void* a, const void* b, const void* c, F f, int64_t n) {
+    constexpr int V = 16 / sizeof(T);
+    const int64_t TILE = (int64_t)kEwThreads * kEwUnroll * V;
+    int64_t tiles = (n + TILE - 1) / TILE;
+    int64_t cap = (int64_t)sm_count(st->dev) * 8;
+    unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    auto al = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    int vec_ok = al(out) && al(a) && al(b) && al(c);
+    ew_stream_kernel<T, F, NIN><<<grid, kEwThreads, 0, st->s>>>(
+        (T*)out, (const T*)a, (const T*)b, (const T*)c, f, n, vec_ok);
+}
+
+// ---- host: pattern matching on the compiled program ----------------------------------------------------
+struct Node { int op, arg, kid[3], nk; };
+
+static int build_tree(const ProgramDesc& P, std::vector<Node>& nodes) {
+    std::vector<int> stk;
+    for (int pc = 0; pc < P.ninstr; ++pc) {
+        Node nd{P.code[2 * pc], P.code[2 * pc + 1], {-1, -1, -1}, 0};
+        int need = 0;
+        switch (nd.op) {
+            case B200_OP_LEAF: need = 0; break;
+            case B200_OP_CONVERT: case B200_OP_ABS: case B200_OP_ABS2: case B200_OP_EXP: case B200_OP_NEG: need = 1; break;
+            case B200_OP_MULADD: need = 3; break;
+            default: need = 2; break;
+        }
+        for (int k = need - 1; k >= 0; --k) { nd.kid[k] = stk.back(); stk.pop_back(); }
+        nd.nk = need;
+        nodes.push_back(nd);
+        stk.push_back((int)nodes.size() - 1);
+    }
+    return stk.back();
+}
+
+template <typename T>
+static typename Elem<T>::C scalar_as(uint64_t cls) {
+    using C = typename Elem<T>::C;
+    if (sizeof(C) == 4) { uint32_t u = (uint32_t)cls; float f; memcpy(&f, &u, 4); return (C)f; }
+    double d; memcpy(&d, &cls, 8); return (C)d;
+}
+
+template <typename T>
+static bool try_fixed(b200_stream_t st, const Compiled& C, const std::vector<Node>& N, int root, void* out, int64_t n) {
+    const ProgramDesc& P = C.P;
+    auto is_arr = [&](int i) { return i >= 0 && N[i].op == B200_OP_LEAF && !P.leaves[N[i].arg].is_scalar; };
+    auto is_sc = [&](int i) { return i >= 0 && N[i].op == B200_OP_LEAF && P.leaves[N[i].arg].is_scalar; };
+    auto ptr = [&](int i) { return P.leaves[N[i].arg].ptr; };
+    const Node& r = N[root];
+    if (r.op != B200_OP_ADD) return false;
+    for (int side = 0; side < 2; ++side) {
+        const int m = r.kid[side], o = r.kid[1 - side];
+        if (m < 0 || N[m].op != B200_OP_MUL) continue;
+        const int p = N[m].kid[0], q = N[m].kid[1];
+        // a*x + y
+        if (is_arr(o) && ((is_sc(p) && is_arr(q)) || (is_arr(p) && is_sc(q)))) {
+            const int s = is_sc(p) ? p : q, x = is_sc(p) ? q : p;
+            AxpyF<T> f{scalar_as<T>(P.leaves[N[s].arg].scalar)};
+            launch_stream<T, AxpyF<T>, 2>(st, out, ptr(x), ptr(o), nullptr, f, n);
+            return true;
+        }
+        // x*y + exp(-abs(z))
+        if (is_arr(p) && is_arr(q) && N[o].op == B200_OP_EXP) {
+            const int ng = N[o].kid[0];
+            if (N[ng].op != B200_OP_NEG) continue;
+            const int ab = N[ng].kid[0];
+            if (N[ab].op != B200_OP_ABS || !is_arr(N[ab].kid[0])) continue;
+            launch_stream<T, MulAddExpNegAbsF<T>, 3>(st, out, ptr(p), ptr(q), ptr(N[ab].kid[0]), MulAddExpNegAbsF<T>{}, n);
+            return true;
+        }
+    }
+    return false;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, const b200_leaf* leaves,
+                                  int32_t nleaves, const uint8_t* program, int32_t ninstr) {
+    B200_TRY(enter(st));
+    B200_TRY(check_tensor(out, "broadcast destination"));
+    const int64_t n = tensor_numel(out);
+    Compiled C;
+    B200_TRY(compile_program(out->shape, out->ndim, leaves, nleaves, program, ninstr, out->dtype, &C));
+    if (n == 0) return B200_OK;
+    for (int d = 0; d < out->ndim; ++d)
+        if (out->shape[d] > 1 && out->stride[d] == 0) return fail(B200_INVALID_ARG, "broadcast destination has a zero stride");
+
+    LeafDesc O{};
+    O.ptr = out->ptr;
+    O.dtype = out->dtype;
+    for (int d = 0; d < out->ndim; ++d) O.stride[d] = out->shape[d] == 1 ? 0 : out->stride[d];
+    const bool out_dense = tensor_is_contiguous(out);
+    if (!out_dense) C.P.linear = 0;
+    if (!C.P.linear || reinterpret_cast<uintptr_t>(out->ptr) % (dtype_size(out->dtype) * kVec) != 0) C.P.vec_ok = 0;
+
+    // Hard-wired kernels: every array leaf dense, same dtype as the destination, no conversions.
+    if (C.P.linear) {
+        bool uniform = true;
+        for (int k = 0; k < nleaves; ++k) if (C.P.leaves[k].dtype != out->dtype) uniform = false;
+        for (int pc = 0; pc < C.P.ninstr; ++pc) if (C.P.code[2 * pc] == B200_OP_CONVERT) uniform = false;
+        if (uniform) {
+            std::vector<Node> nodes;
+            int root = build_tree(C.P, nodes);
+            bool done = false;
+            switch (out->dtype) {
+                case B200_F32: done = try_fixed<float>(st, C, nodes, root, out->ptr, n); break;
+                case B200_F64: done = try_fixed<double>(st, C, nodes, root, out->ptr, n); break;
+                case B200_F16: done = try_fixed<__half>(st, C, nodes, root, out->ptr, n); break;
+                case B200_BF16: done = try_fixed<__nv_bfloat16>(st, C, nodes, root, out->ptr, n); break;
+                default: break;
+            }
+            if (done) return finish(st, "b200_broadcast");
+        }
+    }
+
+    const int64_t nvec = (n + kVec - 1) / kVec;
+    int64_t blocks = (nvec + 255) / 256;
+    const int64_t cap = (int64_t)sm_count(st->dev) * 8;
+    if (blocks > cap) blocks = cap;
+    if (C.wide) ew_program_kernel<true><<<(unsigned)blocks, 256, 0, st->s>>>(C.P, O, n);
+    else ew_program_kernel<false><<<(unsigned)blocks, 256, 0, st->s>>>(C.P, O, n);
+    return finish(st, "b200_broadcast");
+}

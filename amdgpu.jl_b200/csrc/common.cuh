@@ -1,0 +1,141 @@
+// Internal declarations shared by the translation units of libb200arrays.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string>
+
+#include "../../include/b200arrays.h"
+
+// ---- host-side handles ---------------------------------------------------------------------
+struct b200_stream_s {
+    int          dev;
+    cudaStream_t s;
+    bool         owned;
+    // Scratch owned by the stream: operators launched on one stream run in order, so one
+    // buffer per stream can be reused by every call without extra synchronisation.
+    void*        scratch;
+    size_t       scratch_bytes;
+};
+
+struct b200_event_s {
+    int         dev;
+    cudaEvent_t e;
+};
+
+namespace b200 {
+
+// Thread-local error text; returns `code` so call sites can `return fail(...)`.
+int32_t fail(int32_t code, const char* fmt, ...);
+int32_t cuda_fail(cudaError_t e, const char* what);
+
+#define B200_CUDA(expr)                                                  \
+    do {                                                                 \
+        cudaError_t _e = (expr);                                         \
+        if (_e != cudaSuccess) return ::b200::cuda_fail(_e, #expr);      \
+    } while (0)
+
+#define B200_TRY(expr)                                                   \
+    do {                                                                 \
+        int32_t _s = (expr);                                             \
+        if (_s != B200_OK) return _s;                                    \
+    } while (0)
+
+// Makes the stream's device current; validates the handle.
+int32_t enter(b200_stream_t st);
+// Returns at least `bytes` of stream-owned scratch (256-byte aligned).  The first
+// kCounterBytes of every scratch buffer hold ticket counters that are zero between kernels
+// (the last block to take a ticket resets it); `counters` receives that region.
+constexpr size_t kCounterBytes = 64 * 1024;
+int32_t scratch(b200_stream_t st, size_t bytes, void** out, unsigned int** counters = nullptr);
+// Device pointer of this device's latched error word (kernels store a status code there).
+int32_t* device_error_word(int dev);
+// Called by every operator after its launches: launch-error check + optional blocking mode.
+int32_t finish(b200_stream_t st, const char* what);
+int sm_count(int dev);
+
+inline size_t dtype_size(int32_t dt) {
+    switch (dt) {
+        case B200_F16: case B200_BF16: case B200_I16: case B200_U16: return 2;
+        case B200_F32: case B200_I32: case B200_U32: return 4;
+        case B200_F64: case B200_I64: case B200_U64: return 8;
+        case B200_I8: case B200_U8: case B200_BOOL: return 1;
+        default: return 0;
+    }
+}
+inline bool dtype_is_float(int32_t dt) { return dt >= B200_F16 && dt <= B200_F64; }
+inline bool dtype_is_signed_int(int32_t dt) { return dt >= B200_I8 && dt <= B200_I64; }
+inline bool dtype_is_unsigned_int(int32_t dt) { return dt >= B200_U8 && dt <= B200_BOOL; }
+
+inline int64_t tensor_numel(const b200_tensor* t) {
+    int64_t n = 1;
+    for (int d = 0; d < t->ndim; ++d) n *= t->shape[d];
+    return n;
+}
+// Dense column-major (stride[0]==1, stride[d]==stride[d-1]*shape[d-1]); extents of 1 are free.
+inline bool tensor_is_contiguous(const b200_tensor* t) {
+    int64_t expect = 1;
+    for (int d = 0; d < t->ndim; ++d) {
+        if (t->shape[d] != 1 && t->stride[d] != expect) return false;
+        expect *= t->shape[d];
+    }
+    return true;
+}
+int32_t check_tensor(const b200_tensor* t, const char* name);
+
+}  // namespace b200
+
+// ---- device-side helpers --------------------------------------------------------------------
+#ifdef __CUDACC__
+namespace b200 {
+
+// 16-byte vector of T for 128-bit global accesses.
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Vec {
+    T v[N];
+};
+
+// Streaming global accesses: inputs are read once, outputs written once.
+template <typename V>
+__device__ __forceinline__ V ld_stream(const V* p) {
+    return __ldcs(p);
+}
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void st_stream16(void* p, uint4 v) {
+    __stcs(reinterpret_cast<uint4*>(p), v);
+}
+
+// Records a device-side failure in the device's latched error word (pinned host memory that
+// the host inspects at the next synchronisation).  Spinning kernels poll it on their slow
+// path so that one timed-out wait ends every other wait quickly.
+__device__ __forceinline__ void latch_error(int32_t* word, int32_t code) {
+    *(volatile int32_t*)word = code;
+    __threadfence_system();
+}
+__device__ __forceinline__ bool error_latched(const int32_t* word) {
+    return *(volatile const int32_t*)word != 0;
+}
+
+// Julia Base.max/min on floats: NaN wins, -0.0 orders below +0.0.
+template <typename F>
+__device__ __forceinline__ F jl_max(F a, F b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    if (a == b) return signbit(a) ? b : a;
+    return a > b ? a : b;
+}
+template <typename F>
+__device__ __forceinline__ F jl_min(F a, F b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    if (a == b) return signbit(a) ? a : b;
+    return a < b ? a : b;
+}
+
+}  // namespace b200
+#endif

@@ -1,0 +1,725 @@
+// mapreduce with dims: R[Iother] = op over Ireduce of f(A[I]).
+//
+// Takes the place of GPUArrays.mapreducedim! as implemented in src/kernels/mapreduce.jl:86-173
+// of the reference (partial_mapreduce_device :43-82, reduce_group :8-34).  Where the reference
+// needs up to three launches and two pool temporaries for one scalar (a 256-wide LDS tree per
+// group, recursion over the partials), every path here is ONE launch: threads fold 128-bit
+// vectors into registers, warps combine by shuffle, blocks through one shared-memory hop, and
+// when several blocks share an output the last one to take a ticket folds their partials in a
+// fixed order - results are reproducible run to run.
+//
+// Index spaces are collapsed to (K, L, M): K kept elements that are contiguous in memory, L
+// reduced, M kept outer.  K == 1 streams contiguous runs (dims = leading dimensions, or all);
+// K > 1 maps threads along K so that loads stay coalesced while each thread walks the strided
+// reduced dimension (dims = 2 of a column-major matrix).  Anything else - a whole broadcast
+// tree as the mapped function, several operands, gaps in the reduced dimensions, strided
+// views - goes through the program evaluator.  Algorithmic traffic: sizeof(T) per input
+// element plus the outputs.
+#include "program.cuh"
+
+#include <cstring>
+#include <limits>
+#include <type_traits>
+
+namespace b200 {
+
+enum { MAP_ID = 0, MAP_ABS = 1, MAP_ABS2 = 2 };
+constexpr int kRedThreads = 256;
+
+// ---- operator algebra ---------------------------------------------------------------------------------
+template <typename Acc, int OP>
+__device__ __forceinline__ Acc red_identity() {
+    if constexpr (OP == B200_RED_ADD) return Acc(0);
+    else if constexpr (OP == B200_RED_MUL) return Acc(1);
+    else if constexpr (OP == B200_RED_MAX) {
+        if constexpr (std::is_floating_point<Acc>::value) return -std::numeric_limits<Acc>::infinity();
+        else return std::numeric_limits<Acc>::lowest();
+    } else {
+        if constexpr (std::is_floating_point<Acc>::value) return std::numeric_limits<Acc>::infinity();
+        else return std::numeric_limits<Acc>::max();
+    }
+}
+template <typename Acc, int OP>
+__device__ __forceinline__ Acc red_apply(Acc a, Acc b) {
+    using A = Arith<Acc>;
+    if constexpr (OP == B200_RED_ADD) return A::add(a, b);
+    else if constexpr (OP == B200_RED_MUL) return A::mul(a, b);
+    else if constexpr (OP == B200_RED_MAX) return A::max(a, b);
+    else return A::min(a, b);
+}
+
+template <typename T> struct InClass { using type = T; };
+template <> struct InClass<__half> { using type = float; };
+template <> struct InClass<__nv_bfloat16> { using type = float; };
+template <typename T> __device__ __forceinline__ typename InClass<T>::type widen(T v) { return v; }
+template <> __device__ __forceinline__ float widen<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// f is applied in the element's own arithmetic class, then the value widens to the accumulator.
+template <typename Tin, typename Acc, int MAP>
+__device__ __forceinline__ Acc map_elem(Tin x) {
+    using C = typename InClass<Tin>::type;
+    C v = widen(x);
+    if constexpr (MAP == MAP_ABS) v = Arith<C>::abs(v);
+    else if constexpr (MAP == MAP_ABS2) v = Arith<C>::mul(v, v);
+    return (Acc)v;
+}
+
+template <typename Acc>
+__device__ __forceinline__ void store_result(void* R, int dt, int64_t idx, Acc v) {
+    store_bits(R, dtype_bytes(dt), idx, encode<uint64_t>(dt, raw_of<uint64_t>(v)));
+}
+template <typename Acc>
+__device__ __forceinline__ Acc load_result(const void* R, int dt, int64_t idx) {
+    return as_c<Acc, uint64_t>(decode<uint64_t>(dt, load_bits(R, dtype_bytes(dt), idx)));
+}
+
+template <typename Acc, int OP>
+__device__ __forceinline__ Acc warp_reduce(Acc v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = red_apply<Acc, OP>(v, __shfl_down_sync(0xffffffffu, v, off));
+    return v;
+}
+// Result valid in thread 0.  `smem` holds 32 values.
+template <typename Acc, int OP>
+__device__ __forceinline__ Acc block_reduce(Acc v, Acc* smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_reduce<Acc, OP>(v);
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < nwarps ? smem[lane] : red_identity<Acc, OP>();
+        v = warp_reduce<Acc, OP>(v);
+    }
+    __syncthreads();
+    return v;
+}
+
+// Folds n contiguous elements starting at p into acc[0..V), cooperatively over `nthr` threads.
+template <typename Tin, typename Acc, int MAP, int OP, int V>
+__device__ __forceinline__ void segment_accumulate(const Tin* p, int64_t n, int tid, int nthr, Acc acc[V]) {
+    using VT = Vec<Tin, V>;
+    int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) / sizeof(Tin));
+    if (head > n) head = n;
+    if (tid < head) acc[0] = red_apply<Acc, OP>(acc[0], map_elem<Tin, Acc, MAP>(p[tid]));
+    const uint4* vp = reinterpret_cast<const uint4*>(p + head);
+    const int64_t nv = (n - head) / V;
+    constexpr int U = 4;
+    int64_t i = tid;
+    for (; i + (int64_t)(U - 1) * nthr < nv; i += (int64_t)U * nthr) {
+        VT v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = __builtin_bit_cast(VT, __ldcs(vp + i + (int64_t)u * nthr));
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v[u].v[k]));
+    }
+    for (; i < nv; i += nthr) {
+        VT v = __builtin_bit_cast(VT, __ldcs(vp + i));
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v.v[k]));
+    }
+    const int64_t done = head + nv * V;
+    if (tid < n - done) acc[0] = red_apply<Acc, OP>(acc[0], map_elem<Tin, Acc, MAP>(p[done + tid]));
+}
+
+template <typename Acc, int OP, int V>
+__device__ __forceinline__ Acc fold_lanes(const Acc acc[V]) {
+    Acc r = acc[0];
+#pragma unroll
+    for (int k = 1; k < V; ++k) r = red_apply<Acc, OP>(r, acc[k]);
+    return r;
+}
+
+struct RedOut {
+    void*    R;
+    int32_t  rdtype;
+    int32_t  use_init;
+    uint64_t init;      // class bits of the accumulator type
+};
+
+template <typename Acc, int OP>
+__device__ __forceinline__ void finalize(const RedOut& o, int64_t idx, Acc v) {
+    Acc seed = o.use_init ? as_c<Acc, uint64_t>(o.init) : load_result<Acc>(o.R, o.rdtype, idx);
+    store_result<Acc>(o.R, o.rdtype, idx, red_apply<Acc, OP>(seed, v));
+}
+
+// (map, op) pairs with a statically specialised inner loop; everything else uses the evaluator.
+#define B200_MAPOP(MAPV, OPV) ((MAPV) * 4 + (OPV))
+#define B200_MAPOP_SWITCH(mapop, CALL)                                                             \
+    switch (mapop) {                                                                               \
+        case B200_MAPOP(MAP_ID, B200_RED_ADD): CALL(MAP_ID, B200_RED_ADD); break;                  \
+        case B200_MAPOP(MAP_ID, B200_RED_MUL): CALL(MAP_ID, B200_RED_MUL); break;                  \
+        case B200_MAPOP(MAP_ID, B200_RED_MAX): CALL(MAP_ID, B200_RED_MAX); break;                  \
+        case B200_MAPOP(MAP_ID, B200_RED_MIN): CALL(MAP_ID, B200_RED_MIN); break;                  \
+        case B200_MAPOP(MAP_ABS, B200_RED_ADD): CALL(MAP_ABS, B200_RED_ADD); break;                \
+        case B200_MAPOP(MAP_ABS, B200_RED_MAX): CALL(MAP_ABS, B200_RED_MAX); break;                \
+        case B200_MAPOP(MAP_ABS, B200_RED_MIN): CALL(MAP_ABS, B200_RED_MIN); break;                \
+        case B200_MAPOP(MAP_ABS2, B200_RED_ADD): CALL(MAP_ABS2, B200_RED_ADD); break;              \
+        default: break;                                                                            \
+    }
+static bool mapop_supported(int map, int op) {
+    if (map == MAP_ID) return true;
+    if (map == MAP_ABS) return op != B200_RED_MUL;
+    return op == B200_RED_ADD;
+}
+
+// ---- K == 1: contiguous runs --------------------------------------------------------------------------
+// One block per (column, chunk).  With B > 1 chunks per column the last block to finish a column
+// folds the B partials.
+template <typename Tin, typename Acc, int MAP, int OP>
+__device__ __forceinline__ void contig_block_body(const Tin* A, int64_t L, int64_t M, int B, int64_t chunk,
+                                                  Acc* partials, unsigned int* counters, const RedOut& out) {
+    constexpr int V = 16 / sizeof(Tin);
+    __shared__ Acc smem[32];
+    __shared__ int s_last;
+    const int64_t items = M * B;
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const int64_t m = item / B;
+        const int b = (int)(item - m * B);
+        const int64_t beg = (int64_t)b * chunk;
+        int64_t end = beg + chunk;
+        if (end > L) end = L;
+        Acc acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = red_identity<Acc, OP>();
+        if (end > beg) segment_accumulate<Tin, Acc, MAP, OP, V>(A + m * L + beg, end - beg, threadIdx.x, blockDim.x, acc);
+        Acc v = block_reduce<Acc, OP>(fold_lanes<Acc, OP, V>(acc), smem);
+        if (B == 1) {
+            if (threadIdx.x == 0) finalize<Acc, OP>(out, m, v);
+            continue;
+        }
+        if (threadIdx.x == 0) {
+            partials[m * B + b] = v;
+            __threadfence();
+            const unsigned int t = atomicAdd(&counters[m], 1u);
+            s_last = (t == (unsigned int)(B - 1));
+            if (s_last) counters[m] = 0;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            Acc p = red_identity<Acc, OP>();
+            for (int j = threadIdx.x; j < B; j += blockDim.x) p = red_apply<Acc, OP>(p, __ldcg(&partials[m * B + j]));
+            p = block_reduce<Acc, OP>(p, smem);
+            if (threadIdx.x == 0) finalize<Acc, OP>(out, m, p);
+        }
+        __syncthreads();
+    }
+}
+
+template <typename Tin, typename Acc>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_contig_block_kernel(const Tin* A, int64_t L, int64_t M, int B, int64_t chunk, int mapop,
+                           Acc* partials, unsigned int* counters, RedOut out) {
+#define CALL(MAPV, OPV) contig_block_body<Tin, Acc, MAPV, OPV>(A, L, M, B, chunk, partials, counters, out)
+    B200_MAPOP_SWITCH(mapop, CALL)
+#undef CALL
+}
+
+// One warp per column.
+template <typename Tin, typename Acc, int MAP, int OP>
+__device__ __forceinline__ void contig_warp_body(const Tin* A, int64_t L, int64_t M, const RedOut& out) {
+    constexpr int V = 16 / sizeof(Tin);
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t m = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); m < M; m += nwarps) {
+        Acc acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = red_identity<Acc, OP>();
+        segment_accumulate<Tin, Acc, MAP, OP, V>(A + m * L, L, lane, 32, acc);
+        Acc v = warp_reduce<Acc, OP>(fold_lanes<Acc, OP, V>(acc));
+        if (lane == 0) finalize<Acc, OP>(out, m, v);
+    }
+}
+template <typename Tin, typename Acc>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_contig_warp_kernel(const Tin* A, int64_t L, int64_t M, int mapop, RedOut out) {
+#define CALL(MAPV, OPV) contig_warp_body<Tin, Acc, MAPV, OPV>(A, L, M, out)
+    B200_MAPOP_SWITCH(mapop, CALL)
+#undef CALL
+}
+
+// One thread per column (very short columns; neighbouring threads read neighbouring columns).
+template <typename Tin, typename Acc, int MAP, int OP>
+__device__ __forceinline__ void contig_thread_body(const Tin* A, int64_t L, int64_t M, const RedOut& out) {
+    const int64_t nthr = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; m < M; m += nthr) {
+        Acc v = red_identity<Acc, OP>();
+        const Tin* p = A + m * L;
+        for (int64_t l = 0; l < L; ++l) v = red_apply<Acc, OP>(v, map_elem<Tin, Acc, MAP>(p[l]));
+        finalize<Acc, OP>(out, m, v);
+    }
+}
+template <typename Tin, typename Acc>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_contig_thread_kernel(const Tin* A, int64_t L, int64_t M, int mapop, RedOut out) {
+#define CALL(MAPV, OPV) contig_thread_body<Tin, Acc, MAPV, OPV>(A, L, M, out)
+    B200_MAPOP_SWITCH(mapop, CALL)
+#undef CALL
+}
+
+// ---- K > 1: strided reduced dimension ---------------------------------------------------------------
+struct StridedPlan {
+    int64_t K, L, M;
+    int     kx, ly;        // threads along K (each owning V consecutive k) and along L
+    int64_t LS;            // rows per strip
+    int     nstrips;
+    int64_t kblocks;
+};
+
+template <typename Tin, typename Acc, int MAP, int OP, int V>
+__device__ __forceinline__ void strided_body(const Tin* A, const StridedPlan& pl, Acc* partials,
+                                             unsigned int* counters, const RedOut& out, Acc* smem) {
+    using VT = Vec<Tin, V>;
+    __shared__ int s_last;
+    const int tx = threadIdx.x % pl.kx, ty = threadIdx.x / pl.kx;
+    const bool lane_on = ty < pl.ly;
+    const int64_t items = pl.kblocks * pl.nstrips * pl.M;
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const int64_t kb = item % pl.kblocks;
+        const int64_t rest = item / pl.kblocks;
+        const int strip = (int)(rest % pl.nstrips);
+        const int64_t m = rest / pl.nstrips;
+        const int64_t k0 = (kb * pl.kx + tx) * V;
+        const bool on = lane_on && k0 < pl.K;
+        const int64_t lbeg = (int64_t)strip * pl.LS;
+        int64_t lend = lbeg + pl.LS;
+        if (lend > pl.L) lend = pl.L;
+        Acc acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = red_identity<Acc, OP>();
+        if (on) {
+            const Tin* base = A + k0 + pl.K * (pl.L * m);
+            constexpr int U = 4;
+            int64_t l = lbeg + ty;
+            for (; l + (int64_t)(U - 1) * pl.ly < lend; l += (int64_t)U * pl.ly) {
+                VT v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const Tin* p = base + pl.K * (l + (int64_t)u * pl.ly);
+                    if constexpr (V * sizeof(Tin) == 16) v[u] = __builtin_bit_cast(VT, __ldcs(reinterpret_cast<const uint4*>(p)));
+                    else v[u].v[0] = *p;
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v[u].v[k]));
+            }
+            for (; l < lend; l += pl.ly) {
+                const Tin* p = base + pl.K * l;
+                VT v;
+                if constexpr (V * sizeof(Tin) == 16) v = __builtin_bit_cast(VT, __ldcs(reinterpret_cast<const uint4*>(p)));
+                else v.v[0] = *p;
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v.v[k]));
+            }
+        }
+        // combine the ly row groups through shared memory, in row-group order
+        if (lane_on) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) smem[(ty * pl.kx + tx) * V + k] = acc[k];
+        }
+        __syncthreads();
+        if (ty == 0) {
+            for (int y = 1; y < pl.ly; ++y)
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], smem[(y * pl.kx + tx) * V + k]);
+        }
+        const int64_t tile = m * pl.kblocks + kb;
+        if (pl.nstrips == 1) {
+            if (ty == 0 && k0 < pl.K) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) finalize<Acc, OP>(out, k0 + k + pl.K * m, acc[k]);
+            }
+            __syncthreads();
+            continue;
+        }
+        const int64_t width = (int64_t)pl.kx * V;
+        if (ty == 0) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) partials[(tile * pl.nstrips + strip) * width + tx * V + k] = acc[k];
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int t = atomicAdd(&counters[tile], 1u);
+            s_last = (t == (unsigned int)(pl.nstrips - 1));
+            if (s_last) counters[tile] = 0;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            if (ty == 0 && k0 < pl.K) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    Acc p = red_identity<Acc, OP>();
+                    for (int s = 0; s < pl.nstrips; ++s)
+                        p = red_apply<Acc, OP>(p, __ldcg(&partials[(tile * pl.nstrips + s) * width + tx * V + k]));
+                    finalize<Acc, OP>(out, k0 + k + pl.K * m, p);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <typename Tin, typename Acc, int V>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_strided_kernel(const Tin* A, StridedPlan pl, int mapop, Acc* partials, unsigned int* counters, RedOut out) {
+    __shared__ Acc smem[kRedThreads * V];
+#define CALL(MAPV, OPV) strided_body<Tin, Acc, MAPV, OPV, V>(A, pl, partials, counters, out, smem)
+    B200_MAPOP_SWITCH(mapop, CALL)
+#undef CALL
+}
+
+// ---- evaluator path -------------------------------------------------------------------------------------
+struct GenericPlan {
+    int64_t n_out, n_red;
+    int     B;             // blocks per output
+    int64_t chunk;         // reduced elements per block
+    uint32_t reduced_mask; // bit d set: dimension d is reduced
+    int32_t full;          // every dimension reduced: index = r, linear access allowed
+    int32_t redop, acc_dtype;
+    uint64_t identity;     // class bits
+};
+
+template <typename C, typename R>
+__device__ __forceinline__ R red_raw_c(int redop, R a, R b) {
+    using A = Arith<C>;
+    const C x = as_c<C>(a), y = as_c<C>(b);
+    switch (redop) {
+        case B200_RED_ADD: return raw_of<R>(A::add(x, y));
+        case B200_RED_MUL: return raw_of<R>(A::mul(x, y));
+        case B200_RED_MAX: return raw_of<R>(A::max(x, y));
+        default: return raw_of<R>(A::min(x, y));
+    }
+}
+template <bool WIDE, typename R>
+__device__ __forceinline__ R red_raw(int redop, int cls, R a, R b) {
+    switch (cls) {
+        case CF32: return red_raw_c<float>(redop, a, b);
+        case CI32: return red_raw_c<int32_t>(redop, a, b);
+        case CU32: return red_raw_c<uint32_t>(redop, a, b);
+        default:
+            if constexpr (WIDE) {
+                if (cls == CF64) return red_raw_c<double>(redop, a, b);
+                if (cls == CI64) return red_raw_c<int64_t>(redop, a, b);
+                return red_raw_c<uint64_t>(redop, a, b);
+            }
+            return a;
+    }
+}
+
+template <bool WIDE>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_program_kernel(const __grid_constant__ ProgramDesc P, const __grid_constant__ LeafDesc O,
+                      const __grid_constant__ GenericPlan G, typename RawOf<WIDE>::type* partials,
+                      unsigned int* counters, RedOut out) {
+    using R = typename RawOf<WIDE>::type;
+    __shared__ R smem[kRedThreads];
+    __shared__ int s_last;
+    const int cls = dtype_class(G.acc_dtype);
+    const int64_t items = G.n_out * G.B;
+    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const int64_t o = item / G.B;
+        const int b = (int)(item - o * G.B);
+        const int64_t rbeg = (int64_t)b * G.chunk;
+        int64_t rend = rbeg + G.chunk;
+        if (rend > G.n_red) rend = G.n_red;
+        R acc = (R)G.identity;
+        for (int64_t r = rbeg + (int64_t)threadIdx.x * kVec; r < rend; r += (int64_t)blockDim.x * kVec) {
+            const int64_t left = rend - r;
+            const int nvalid = left < kVec ? (int)left : kVec;
+            int64_t lin[kVec];
+            if (G.full) {
+#pragma unroll
+                for (int j = 0; j < kVec; ++j) lin[j] = r + j;
+            } else {
+#pragma unroll
+                for (int j = 0; j < kVec; ++j) {
+                    int64_t rr = r + j, oo = o, mult = 1, li = 0;
+                    for (int d = 0; d < P.ndim; ++d) {
+                        const int64_t e = P.shape[d];
+                        int64_t idx;
+                        if ((G.reduced_mask >> d) & 1u) { idx = rr % e; rr /= e; }
+                        else { idx = oo % e; oo /= e; }
+                        li += idx * mult;
+                        mult *= e;
+                    }
+                    lin[j] = li;
+                }
+            }
+            R res[kVec];
+            eval_program<WIDE>(P, lin, nvalid, res);
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) if (j < nvalid) acc = red_raw<WIDE, R>(G.redop, cls, acc, res[j]);
+        }
+        smem[threadIdx.x] = acc;
+        __syncthreads();
+        for (int s = kRedThreads / 2; s > 0; s >>= 1) {
+            if ((int)threadIdx.x < s) smem[threadIdx.x] = red_raw<WIDE, R>(G.redop, cls, smem[threadIdx.x], smem[threadIdx.x + s]);
+            __syncthreads();
+        }
+        R v = smem[0];
+        __syncthreads();
+        bool write = (G.B == 1);
+        if (G.B > 1) {
+            if (threadIdx.x == 0) {
+                partials[o * G.B + b] = v;
+                __threadfence();
+                const unsigned int t = atomicAdd(&counters[o], 1u);
+                s_last = (t == (unsigned int)(G.B - 1));
+                if (s_last) counters[o] = 0;
+            }
+            __syncthreads();
+            if (s_last && threadIdx.x == 0) {
+                __threadfence();
+                v = (R)G.identity;
+                for (int j = 0; j < G.B; ++j) v = red_raw<WIDE, R>(G.redop, cls, v, __ldcg(&partials[o * G.B + j]));
+                write = true;
+            }
+            __syncthreads();
+        }
+        if (write && threadIdx.x == 0) {
+            // offset of output o inside R (reduced dimensions have extent 1 there)
+            int64_t oo = o, off = 0;
+            for (int d = 0; d < P.ndim; ++d) {
+                if ((G.reduced_mask >> d) & 1u) continue;
+                const int64_t e = P.shape[d];
+                off += (oo % e) * O.stride[d];
+                oo /= e;
+            }
+            const int bytes = dtype_bytes(O.dtype);
+            R seed = out.use_init ? (R)out.init : decode<R>(O.dtype, load_bits(O.ptr, bytes, off));
+            v = red_raw<WIDE, R>(G.redop, cls, seed, v);
+            store_bits(const_cast<void*>(O.ptr), bytes, off, encode<R>(O.dtype, v));
+        }
+    }
+}
+
+// ---- host ------------------------------------------------------------------------------------------------
+static int acc_dtype_of(int rdtype) {
+    switch (dtype_class(rdtype)) {
+        case CF32: return B200_F32;
+        case CF64: return B200_F64;
+        case CI32: return B200_I32;
+        case CI64: return B200_I64;
+        case CU32: return B200_U32;
+        default: return B200_U64;
+    }
+}
+
+static uint64_t identity_bits(int redop, int acc_dtype) {
+    auto f32 = [](float f) { uint32_t u; memcpy(&u, &f, 4); return (uint64_t)u; };
+    auto f64 = [](double d) { uint64_t u; memcpy(&u, &d, 8); return u; };
+    switch (acc_dtype) {
+        case B200_F32:
+            return redop == B200_RED_ADD ? f32(0.f) : redop == B200_RED_MUL ? f32(1.f)
+                 : redop == B200_RED_MAX ? f32(-std::numeric_limits<float>::infinity()) : f32(std::numeric_limits<float>::infinity());
+        case B200_F64:
+            return redop == B200_RED_ADD ? f64(0.) : redop == B200_RED_MUL ? f64(1.)
+                 : redop == B200_RED_MAX ? f64(-std::numeric_limits<double>::infinity()) : f64(std::numeric_limits<double>::infinity());
+        case B200_I32:
+            return redop == B200_RED_ADD ? 0u : redop == B200_RED_MUL ? 1u
+                 : redop == B200_RED_MAX ? (uint64_t)(uint32_t)INT32_MIN : (uint64_t)(uint32_t)INT32_MAX;
+        case B200_I64:
+            return redop == B200_RED_ADD ? 0u : redop == B200_RED_MUL ? 1u
+                 : redop == B200_RED_MAX ? (uint64_t)INT64_MIN : (uint64_t)INT64_MAX;
+        case B200_U32:
+            return redop == B200_RED_ADD ? 0u : redop == B200_RED_MUL ? 1u
+                 : redop == B200_RED_MAX ? 0u : (uint64_t)UINT32_MAX;
+        default:
+            return redop == B200_RED_ADD ? 0u : redop == B200_RED_MUL ? 1u
+                 : redop == B200_RED_MAX ? 0u : UINT64_MAX;
+    }
+}
+
+template <typename Tin, typename Acc>
+static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L, int64_t M, int mapop, const RedOut& out) {
+    const int sms = sm_count(st->dev);
+    const int64_t target = (int64_t)sms * 8;
+    void* scr = nullptr;
+    unsigned int* counters = nullptr;
+    if (K == 1) {
+        if (M > 1 && L <= 16) {
+            int64_t blocks = (M + kRedThreads - 1) / kRedThreads;
+            if (blocks > target) blocks = target;
+            reduce_contig_thread_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
+            return B200_OK;
+        }
+        if (M >= target * 2 && (size_t)L * sizeof(Tin) <= 16384) {
+            int64_t blocks = (M + 7) / 8;
+            if (blocks > target) blocks = target;
+            reduce_contig_warp_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
+            return B200_OK;
+        }
+        // blocks per column: enough to fill the machine, each with at least 64 KiB of input
+        const int64_t min_chunk = (int64_t)(65536 / sizeof(Tin));
+        int64_t B = (target + M - 1) / M;
+        const int64_t maxB = (L + min_chunk - 1) / min_chunk;
+        if (B > maxB) B = maxB;
+        if (B < 1) B = 1;
+        if (B > 1 && (size_t)M * sizeof(unsigned int) > kCounterBytes) B = 1;
+        int64_t chunk = (L + B - 1) / B;
+        const int64_t grain = (int64_t)kRedThreads * (16 / sizeof(Tin));
+        chunk = (chunk + grain - 1) / grain * grain;
+        B = (L + chunk - 1) / chunk;
+        B200_TRY(scratch(st, (size_t)(M * B) * sizeof(Acc), &scr, &counters));
+        int64_t blocks = M * B;
+        if (blocks > target) blocks = target;
+        reduce_contig_block_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>(
+            (const Tin*)A, L, M, (int)B, chunk, mapop, (Acc*)scr, counters, out);
+        return B200_OK;
+    }
+    // strided
+    constexpr int VMAX = 16 / sizeof(Tin);
+    const bool vec = (K % VMAX == 0) && (reinterpret_cast<uintptr_t>(A) % 16 == 0) && K / VMAX >= 8;
+    StridedPlan pl{};
+    pl.K = K; pl.L = L; pl.M = M;
+    const int V = vec ? VMAX : 1;
+    const int64_t kv = (K + V - 1) / V;
+    pl.kx = (int)(kv < 32 ? kv : 32);
+    pl.ly = kRedThreads / pl.kx;
+    if ((int64_t)pl.ly > L) pl.ly = (int)L;
+    pl.kblocks = (kv + pl.kx - 1) / pl.kx;
+    const int64_t base_blocks = pl.kblocks * M;
+    int64_t ns = (target + base_blocks - 1) / base_blocks;
+    const int64_t max_ns = (L + (int64_t)pl.ly * 4 - 1) / ((int64_t)pl.ly * 4);
+    if (ns > max_ns) ns = max_ns;
+    if (ns < 1) ns = 1;
+    if (ns > 1 && (size_t)base_blocks * sizeof(unsigned int) > kCounterBytes) ns = 1;
+    pl.LS = (L + ns - 1) / ns;
+    pl.LS = (pl.LS + pl.ly - 1) / pl.ly * pl.ly;
+    pl.nstrips = (int)((L + pl.LS - 1) / pl.LS);
+    B200_TRY(scratch(st, (size_t)(base_blocks * pl.nstrips * pl.kx * V) * sizeof(Acc), &scr, &counters));
+    int64_t blocks = base_blocks * pl.nstrips;
+    if (blocks > target * 2) blocks = target * 2;
+    if (vec) reduce_strided_kernel<Tin, Acc, VMAX><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
+    else reduce_strided_kernel<Tin, Acc, 1><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
+    return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
+                                  const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
+                                  int32_t ninstr, int32_t op, const void* init) {
+    B200_TRY(enter(st));
+    B200_TRY(check_tensor(R, "mapreduce destination"));
+    if (!shape && ndim > 0) return fail(B200_INVALID_ARG, "mapreduce: null shape");
+    if (ndim < 0 || ndim > B200_MAX_DIMS) return fail(B200_INVALID_ARG, "mapreduce: ndim %d outside [0,%d]", ndim, B200_MAX_DIMS);
+    if (op < 0 || op >= B200_RED_COUNT) return fail(B200_UNSUPPORTED, "mapreduce: unknown operator %d", op);
+    if (R->dtype == B200_BOOL) return fail(B200_UNSUPPORTED, "mapreduce: Bool destinations are not supported");
+    if (R->ndim > ndim) {
+        for (int d = ndim; d < R->ndim; ++d)
+            if (R->shape[d] != 1) return fail(B200_INVALID_ARG, "mapreduce: destination has more dimensions than the input");
+    }
+    uint32_t mask = 0;
+    int64_t n = 1, n_out = 1, n_red = 1;
+    for (int d = 0; d < ndim; ++d) {
+        if (shape[d] < 0) return fail(B200_INVALID_ARG, "mapreduce: negative extent");
+        const int64_t re = d < R->ndim ? R->shape[d] : 1;
+        n *= shape[d];
+        if (re == shape[d]) n_out *= shape[d];
+        else if (re == 1) { mask |= 1u << d; n_red *= shape[d]; }
+        else return fail(B200_INVALID_ARG, "mapreduce: destination extent %lld in dim %d matches neither %lld nor 1 (check_reducedims)", (long long)re, d, (long long)shape[d]);
+    }
+    if (n == 0) return B200_OK;   // empty input: R is returned untouched
+
+    const int acc_dt = acc_dtype_of(R->dtype);
+    Compiled C;
+    B200_TRY(compile_program(shape, ndim, leaves, nleaves, program, ninstr, acc_dt, &C));
+
+    RedOut out{};
+    out.R = R->ptr;
+    out.rdtype = R->dtype;
+    out.use_init = init ? 1 : 0;
+    if (init) {
+        uint64_t bits = 0;
+        memcpy(&bits, init, dtype_size(R->dtype));
+        out.init = scalar_to_class(R->dtype, bits);
+    }
+
+    // ---- fast paths: one dense array, f in {identity, abs, abs2}
+    const ProgramDesc& P = C.P;
+    bool fast = C.n_array_leaves == 1 && P.linear && tensor_is_contiguous(R) && n_red > 1;
+    int map = MAP_ID, leaf = -1, in_dt = -1;
+    if (fast) {
+        int pc = 0;
+        if (P.code[0] != B200_OP_LEAF || P.leaves[P.code[1]].is_scalar) fast = false;
+        else { leaf = P.code[1]; in_dt = P.leaves[leaf].dtype; pc = 1; }
+        if (fast && pc < P.ninstr && (P.code[2 * pc] == B200_OP_ABS || P.code[2 * pc] == B200_OP_ABS2)) {
+            map = P.code[2 * pc] == B200_OP_ABS ? MAP_ABS : MAP_ABS2;
+            ++pc;
+        }
+        if (fast && pc < P.ninstr && P.code[2 * pc] == B200_OP_CONVERT && (P.code[2 * pc + 1] >> 4) == in_dt) ++pc;
+        if (pc != P.ninstr) fast = false;
+        if (fast && !mapop_supported(map, op)) fast = false;
+    }
+    int64_t K = 1, L = 1, M = 1;
+    if (fast) {
+        int i0 = -1, i1 = -1;
+        for (int d = 0; d < ndim; ++d) if (((mask >> d) & 1u) && shape[d] > 1) { if (i0 < 0) i0 = d; i1 = d; }
+        for (int d = i0; d <= i1 && fast; ++d) if (shape[d] > 1 && !((mask >> d) & 1u)) fast = false;
+        if (fast) {
+            for (int d = 0; d < i0; ++d) K *= shape[d];
+            for (int d = i0; d <= i1; ++d) L *= shape[d];
+            for (int d = i1 + 1; d < ndim; ++d) M *= shape[d];
+        }
+    }
+    if (fast) {
+        const void* A = P.leaves[leaf].ptr;
+        const int mapop = B200_MAPOP(map, op);
+        int32_t s = -1;
+        if (in_dt == B200_F32 && acc_dt == B200_F32) s = launch_fast<float, float>(st, A, K, L, M, mapop, out);
+        else if (in_dt == B200_F16 && acc_dt == B200_F32) s = launch_fast<__half, float>(st, A, K, L, M, mapop, out);
+        else if (in_dt == B200_BF16 && acc_dt == B200_F32) s = launch_fast<__nv_bfloat16, float>(st, A, K, L, M, mapop, out);
+        else if (in_dt == B200_F64 && acc_dt == B200_F64) s = launch_fast<double, double>(st, A, K, L, M, mapop, out);
+        else if (in_dt == B200_I32 && acc_dt == B200_I32) s = launch_fast<int32_t, int32_t>(st, A, K, L, M, mapop, out);
+        else if (in_dt == B200_I32 && acc_dt == B200_I64) s = launch_fast<int32_t, int64_t>(st, A, K, L, M, mapop, out);
+        else if (in_dt == B200_I64 && acc_dt == B200_I64) s = launch_fast<int64_t, int64_t>(st, A, K, L, M, mapop, out);
+        if (s >= 0) {
+            B200_TRY(s);
+            return finish(st, "b200_mapreduce");
+        }
+    }
+
+    // ---- evaluator path
+    GenericPlan G{};
+    G.n_out = n_out;
+    G.n_red = n_red;
+    G.reduced_mask = mask;
+    G.full = (n_out == 1) ? 1 : 0;
+    G.redop = op;
+    G.acc_dtype = acc_dt;
+    G.identity = identity_bits(op, acc_dt);
+    if (!G.full) { C.P.linear = 0; C.P.vec_ok = 0; }
+    const int64_t target = (int64_t)sm_count(st->dev) * 8;
+    int64_t B = (target + n_out - 1) / n_out;
+    const int64_t min_chunk = 16384;
+    const int64_t maxB = (n_red + min_chunk - 1) / min_chunk;
+    if (B > maxB) B = maxB;
+    if (B < 1) B = 1;
+    if (B > 1 && (size_t)n_out * sizeof(unsigned int) > kCounterBytes) B = 1;
+    int64_t chunk = (n_red + B - 1) / B;
+    chunk = (chunk + kVec * kRedThreads - 1) / (kVec * kRedThreads) * (kVec * kRedThreads);
+    B = (n_red + chunk - 1) / chunk;
+    G.B = (int)B;
+    G.chunk = chunk;
+    void* scr = nullptr;
+    unsigned int* counters = nullptr;
+    B200_TRY(scratch(st, (size_t)(n_out * B) * 8, &scr, &counters));
+    LeafDesc O{};
+    O.ptr = R->ptr;
+    O.dtype = R->dtype;
+    for (int d = 0; d < ndim; ++d) O.stride[d] = (d < R->ndim && R->shape[d] != 1) ? R->stride[d] : 0;
+    int64_t blocks = n_out * B;
+    if (blocks > target) blocks = target;
+    if (C.wide) reduce_program_kernel<true><<<(unsigned)blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint64_t*)scr, counters, out);
+    else reduce_program_kernel<false><<<(unsigned)blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint32_t*)scr, counters, out);
+    return finish(st, "b200_mapreduce");
+}

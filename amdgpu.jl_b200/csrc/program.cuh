@@ -1,0 +1,433 @@
+// Elementwise programs: host-side validation ("compile") of the postfix byte code that the
+// C ABI accepts, and the device-side evaluator shared by the broadcast and mapreduce kernels.
+//
+// The evaluator is a stack machine whose stack lives in REGISTERS: the stack pointer selects
+// one of a handful of statically indexed code paths, so no slot is ever addressed dynamically
+// and nothing spills to local memory.  Each instruction is decoded once per thread for a
+// vector of kVec consecutive elements.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kVec = 4;        // elements evaluated per thread per decode
+constexpr int kMaxStack = 5;   // deepest value stack a program may need
+constexpr int kPrefetch = 4;   // array leaves whose loads are issued before decoding starts
+
+// Value classes: the arithmetic type an element type computes in.
+enum { CF32 = 0, CF64 = 1, CI32 = 2, CI64 = 3, CU32 = 4, CU64 = 5 };
+
+__host__ __device__ inline int dtype_class(int dt) {
+    switch (dt) {
+        case B200_F16: case B200_BF16: case B200_F32: return CF32;
+        case B200_F64: return CF64;
+        case B200_I8: case B200_I16: case B200_I32: return CI32;
+        case B200_I64: return CI64;
+        case B200_U64: return CU64;
+        default: return CU32;
+    }
+}
+__host__ __device__ inline bool dtype_is_narrow(int dt) {
+    return dt == B200_F16 || dt == B200_BF16 || dt == B200_I8 || dt == B200_I16 ||
+           dt == B200_U8 || dt == B200_U16 || dt == B200_BOOL;
+}
+__host__ __device__ inline int dtype_bytes(int dt) {
+    switch (dt) {
+        case B200_F16: case B200_BF16: case B200_I16: case B200_U16: return 2;
+        case B200_F32: case B200_I32: case B200_U32: return 4;
+        case B200_F64: case B200_I64: case B200_U64: return 8;
+        default: return 1;
+    }
+}
+
+struct LeafDesc {
+    const void* ptr;
+    uint64_t    scalar;                  // class representation (f16 scalar already widened)
+    int64_t     stride[B200_MAX_DIMS];   // elements; 0 in broadcast dims
+    int32_t     dtype;
+    int32_t     is_scalar;
+};
+
+struct ProgramDesc {
+    int32_t  ninstr, nleaves, ndim;
+    int32_t  linear;      // every array leaf is dense with the shape of the index space
+    int32_t  vec_ok;      // ... and 4-element accesses are aligned for every array leaf
+    int32_t  _pad;
+    int64_t  shape[B200_MAX_DIMS];
+    uint8_t  code[2 * (B200_MAX_PROGRAM + 2)];
+    LeafDesc leaves[B200_MAX_LEAVES];
+};
+
+struct Compiled {
+    ProgramDesc P;
+    int32_t result_dtype;   // dtype left on the stack by the last instruction
+    bool    wide;           // some value needs a 64-bit class
+    // Expression tree in postfix order for pattern matching by the operators.
+    int32_t n_array_leaves;
+};
+
+// Validates `program` against `leaves` and the index space `shape`; appends a conversion to
+// `final_dtype` when that is >= 0 and differs from the program's result type.
+int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
+                        int32_t nleaves, const uint8_t* program, int32_t ninstr,
+                        int32_t final_dtype, Compiled* out);
+
+// Converts one scalar between its storage bits and the class representation (host side).
+uint64_t scalar_to_class(int32_t dtype, uint64_t bits);
+uint64_t class_to_storage(int32_t dtype, uint64_t cls);
+
+#ifdef __CUDACC__
+
+template <bool WIDE> struct RawOf { using type = uint32_t; };
+template <> struct RawOf<true> { using type = uint64_t; };
+
+// ---- raw <-> class value ------------------------------------------------------------------------
+template <typename C, typename R> __device__ __forceinline__ C as_c(R r);
+template <> __device__ __forceinline__ float as_c<float, uint32_t>(uint32_t r) { return __uint_as_float(r); }
+template <> __device__ __forceinline__ float as_c<float, uint64_t>(uint64_t r) { return __uint_as_float((uint32_t)r); }
+template <> __device__ __forceinline__ double as_c<double, uint64_t>(uint64_t r) { return __longlong_as_double((long long)r); }
+template <> __device__ __forceinline__ double as_c<double, uint32_t>(uint32_t r) { return (double)__uint_as_float(r); }
+template <> __device__ __forceinline__ int32_t as_c<int32_t, uint32_t>(uint32_t r) { return (int32_t)r; }
+template <> __device__ __forceinline__ int32_t as_c<int32_t, uint64_t>(uint64_t r) { return (int32_t)(uint32_t)r; }
+template <> __device__ __forceinline__ uint32_t as_c<uint32_t, uint32_t>(uint32_t r) { return r; }
+template <> __device__ __forceinline__ uint32_t as_c<uint32_t, uint64_t>(uint64_t r) { return (uint32_t)r; }
+template <> __device__ __forceinline__ int64_t as_c<int64_t, uint64_t>(uint64_t r) { return (int64_t)r; }
+template <> __device__ __forceinline__ int64_t as_c<int64_t, uint32_t>(uint32_t r) { return (int64_t)(int32_t)r; }
+template <> __device__ __forceinline__ uint64_t as_c<uint64_t, uint64_t>(uint64_t r) { return r; }
+template <> __device__ __forceinline__ uint64_t as_c<uint64_t, uint32_t>(uint32_t r) { return r; }
+
+template <typename R> __device__ __forceinline__ R raw_of(float v) { return (R)__float_as_uint(v); }
+template <typename R> __device__ __forceinline__ R raw_of(double v) { return (R)(uint64_t)__double_as_longlong(v); }
+template <typename R> __device__ __forceinline__ R raw_of(int32_t v) { return (R)(uint32_t)v; }
+template <typename R> __device__ __forceinline__ R raw_of(uint32_t v) { return (R)v; }
+template <typename R> __device__ __forceinline__ R raw_of(int64_t v) { return (R)(uint64_t)v; }
+template <typename R> __device__ __forceinline__ R raw_of(uint64_t v) { return (R)v; }
+
+// ---- arithmetic per class (no contraction of separate multiply and add) --------------------------
+template <typename C> struct Arith;
+template <> struct Arith<float> {
+    static __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+    static __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
+    static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+    static __device__ __forceinline__ float div(float a, float b) { return __fdiv_rn(a, b); }
+    static __device__ __forceinline__ float muladd(float a, float b, float c) { return fmaf(a, b, c); }
+    static __device__ __forceinline__ float abs(float a) { return fabsf(a); }
+    static __device__ __forceinline__ float exp(float a) { return expf(a); }
+    static __device__ __forceinline__ float neg(float a) { return -a; }
+    static __device__ __forceinline__ float max(float a, float b) { return jl_max(a, b); }
+    static __device__ __forceinline__ float min(float a, float b) { return jl_min(a, b); }
+};
+template <> struct Arith<double> {
+    static __device__ __forceinline__ double add(double a, double b) { return __dadd_rn(a, b); }
+    static __device__ __forceinline__ double sub(double a, double b) { return __dsub_rn(a, b); }
+    static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
+    static __device__ __forceinline__ double div(double a, double b) { return __ddiv_rn(a, b); }
+    static __device__ __forceinline__ double muladd(double a, double b, double c) { return fma(a, b, c); }
+    static __device__ __forceinline__ double abs(double a) { return fabs(a); }
+    static __device__ __forceinline__ double exp(double a) { return ::exp(a); }
+    static __device__ __forceinline__ double neg(double a) { return -a; }
+    static __device__ __forceinline__ double max(double a, double b) { return jl_max(a, b); }
+    static __device__ __forceinline__ double min(double a, double b) { return jl_min(a, b); }
+};
+template <typename I, typename U, bool SIGNED> struct IntArith {
+    static __device__ __forceinline__ I add(I a, I b) { return (I)((U)a + (U)b); }
+    static __device__ __forceinline__ I sub(I a, I b) { return (I)((U)a - (U)b); }
+    static __device__ __forceinline__ I mul(I a, I b) { return (I)((U)a * (U)b); }
+    static __device__ __forceinline__ I div(I a, I) { return a; }   // rejected by the validator
+    static __device__ __forceinline__ I muladd(I a, I b, I c) { return (I)((U)a * (U)b + (U)c); }
+    static __device__ __forceinline__ I abs(I a) { return (SIGNED && a < 0) ? (I)((U)0 - (U)a) : a; }
+    static __device__ __forceinline__ I exp(I a) { return a; }      // rejected by the validator
+    static __device__ __forceinline__ I neg(I a) { return (I)((U)0 - (U)a); }
+    static __device__ __forceinline__ I max(I a, I b) { return a > b ? a : b; }
+    static __device__ __forceinline__ I min(I a, I b) { return a < b ? a : b; }
+};
+template <> struct Arith<int32_t> : IntArith<int32_t, uint32_t, true> {};
+template <> struct Arith<uint32_t> : IntArith<uint32_t, uint32_t, false> {};
+template <> struct Arith<int64_t> : IntArith<int64_t, uint64_t, true> {};
+template <> struct Arith<uint64_t> : IntArith<uint64_t, uint64_t, false> {};
+
+// Rounds / wraps a class value to a narrow element type (Base computes Float16 in Float32 and
+// rounds after every operation; Int8/Int16 arithmetic wraps).
+template <typename R>
+__device__ __forceinline__ R narrow(int dt, R r) {
+    switch (dt) {
+        case B200_F16: return raw_of<R>(__half2float(__float2half_rn(as_c<float>(r))));
+        case B200_BF16: return raw_of<R>(__bfloat162float(__float2bfloat16_rn(as_c<float>(r))));
+        case B200_I8: return raw_of<R>((int32_t)(int8_t)as_c<int32_t>(r));
+        case B200_I16: return raw_of<R>((int32_t)(int16_t)as_c<int32_t>(r));
+        case B200_U8: return raw_of<R>(as_c<uint32_t>(r) & 0xffu);
+        case B200_U16: return raw_of<R>(as_c<uint32_t>(r) & 0xffffu);
+        case B200_BOOL: return raw_of<R>(as_c<uint32_t>(r) & 1u);
+        default: return r;
+    }
+}
+
+// ---- element <-> class value -----------------------------------------------------------------------
+template <typename R>
+__device__ __forceinline__ R decode(int dt, uint64_t bits) {
+    switch (dt) {
+        case B200_F16: return raw_of<R>(__half2float(__ushort_as_half((unsigned short)bits)));
+        case B200_BF16: return (R)((uint32_t)bits << 16);
+        case B200_I8: return raw_of<R>((int32_t)(int8_t)bits);
+        case B200_I16: return raw_of<R>((int32_t)(int16_t)bits);
+        case B200_U8: case B200_BOOL: return (R)(bits & 0xffu);
+        case B200_U16: return (R)(bits & 0xffffu);
+        case B200_F32: case B200_I32: case B200_U32: return (R)(uint32_t)bits;
+        default: return (R)bits;
+    }
+}
+template <typename R>
+__device__ __forceinline__ uint64_t encode(int dt, R r) {
+    switch (dt) {
+        case B200_F16: return __half_as_ushort(__float2half_rn(as_c<float>(r)));
+        case B200_BF16: return __bfloat16_as_ushort(__float2bfloat16_rn(as_c<float>(r)));
+        default: return (uint64_t)r;   // integer storage keeps the low bytes
+    }
+}
+
+__device__ __forceinline__ uint64_t load_bits(const void* p, int bytes, int64_t off) {
+    switch (bytes) {
+        case 1: return __ldcs(reinterpret_cast<const uint8_t*>(p) + off);
+        case 2: return __ldcs(reinterpret_cast<const uint16_t*>(p) + off);
+        case 4: return __ldcs(reinterpret_cast<const uint32_t*>(p) + off);
+        default: return __ldcs(reinterpret_cast<const unsigned long long*>(p) + off);
+    }
+}
+__device__ __forceinline__ void store_bits(void* p, int bytes, int64_t off, uint64_t v) {
+    switch (bytes) {
+        case 1: reinterpret_cast<uint8_t*>(p)[off] = (uint8_t)v; break;
+        case 2: reinterpret_cast<uint16_t*>(p)[off] = (uint16_t)v; break;
+        case 4: __stcs(reinterpret_cast<uint32_t*>(p) + off, (uint32_t)v); break;
+        default: __stcs(reinterpret_cast<unsigned long long*>(p) + off, (unsigned long long)v); break;
+    }
+}
+
+// Four consecutive elements starting at element `off` (aligned access when `vec`).
+template <typename R>
+__device__ __forceinline__ void load_vec4(const void* p, int dt, int64_t off, bool vec, int nvalid, R out[kVec]) {
+    const int bytes = dtype_bytes(dt);
+    uint64_t b[kVec];
+    if (vec && nvalid == kVec) {
+        switch (bytes) {
+            case 1: { uint32_t w = __ldcs(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p) + off));
+                      b[0] = w & 0xff; b[1] = (w >> 8) & 0xff; b[2] = (w >> 16) & 0xff; b[3] = w >> 24; break; }
+            case 2: { uint2 w = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p) + off));
+                      b[0] = w.x & 0xffff; b[1] = w.x >> 16; b[2] = w.y & 0xffff; b[3] = w.y >> 16; break; }
+            case 4: { uint4 w = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p) + off));
+                      b[0] = w.x; b[1] = w.y; b[2] = w.z; b[3] = w.w; break; }
+            default: { const ulonglong2* q = reinterpret_cast<const ulonglong2*>(reinterpret_cast<const uint64_t*>(p) + off);
+                      ulonglong2 w0 = __ldcs(q), w1 = __ldcs(q + 1);
+                      b[0] = w0.x; b[1] = w0.y; b[2] = w1.x; b[3] = w1.y; break; }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) b[k] = (k < nvalid) ? load_bits(p, bytes, off + k) : 0;
+    }
+#pragma unroll
+    for (int k = 0; k < kVec; ++k) out[k] = decode<R>(dt, b[k]);
+}
+
+template <typename R>
+__device__ __forceinline__ void store_vec4(void* p, int dt, int64_t off, bool vec, int nvalid, const R in[kVec]) {
+    const int bytes = dtype_bytes(dt);
+    uint64_t b[kVec];
+#pragma unroll
+    for (int k = 0; k < kVec; ++k) b[k] = encode<R>(dt, in[k]);
+    if (vec && nvalid == kVec) {
+        switch (bytes) {
+            case 1: { uint32_t w = (uint32_t)(b[0] & 0xff) | ((uint32_t)(b[1] & 0xff) << 8) | ((uint32_t)(b[2] & 0xff) << 16) | ((uint32_t)(b[3] & 0xff) << 24);
+                      *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p) + off) = w; break; }
+            case 2: { uint2 w; w.x = (uint32_t)(b[0] & 0xffff) | ((uint32_t)(b[1] & 0xffff) << 16);
+                      w.y = (uint32_t)(b[2] & 0xffff) | ((uint32_t)(b[3] & 0xffff) << 16);
+                      __stcs(reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p) + off), w); break; }
+            case 4: { uint4 w = make_uint4((uint32_t)b[0], (uint32_t)b[1], (uint32_t)b[2], (uint32_t)b[3]);
+                      __stcs(reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p) + off), w); break; }
+            default: { ulonglong2* q = reinterpret_cast<ulonglong2*>(reinterpret_cast<uint64_t*>(p) + off);
+                      __stcs(q, make_ulonglong2(b[0], b[1])); __stcs(q + 1, make_ulonglong2(b[2], b[3])); break; }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) if (k < nvalid) store_bits(p, bytes, off + k, b[k]);
+    }
+}
+
+// ---- one instruction on statically named stack slots ----------------------------------------------
+// unary: c <- f(c); binary: b <- f(b, c); muladd: a <- a*b+c.  `dt` is the instruction's element
+// type; narrow types are re-rounded / re-wrapped after the operation.
+template <typename C, typename R>
+__device__ __forceinline__ void exec_class(int op, int dt, R* a, R* b, R* c) {
+    using A = Arith<C>;
+    const bool nd = dtype_is_narrow(dt);
+#define B200_CASE(OPC, DST, EXPR)                                   \
+    case OPC:                                                       \
+        _Pragma("unroll") for (int k = 0; k < kVec; ++k) {          \
+            R r = raw_of<R>(EXPR);                                  \
+            if (nd) r = narrow<R>(dt, r);                           \
+            DST[k] = r;                                             \
+        }                                                           \
+        break;
+    switch (op) {
+        B200_CASE(B200_OP_ADD, b, A::add(as_c<C>(b[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_SUB, b, A::sub(as_c<C>(b[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_MUL, b, A::mul(as_c<C>(b[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_DIV, b, A::div(as_c<C>(b[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_MAX, b, A::max(as_c<C>(b[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_MIN, b, A::min(as_c<C>(b[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_MULADD, a, A::muladd(as_c<C>(a[k]), as_c<C>(b[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_ABS, c, A::abs(as_c<C>(c[k])))
+        B200_CASE(B200_OP_ABS2, c, A::mul(as_c<C>(c[k]), as_c<C>(c[k])))
+        B200_CASE(B200_OP_EXP, c, A::exp(as_c<C>(c[k])))
+        B200_CASE(B200_OP_NEG, c, A::neg(as_c<C>(c[k])))
+        default: break;
+    }
+#undef B200_CASE
+}
+
+template <typename S, typename D, typename R>
+__device__ __forceinline__ void convert_class(R* c) {
+#pragma unroll
+    for (int k = 0; k < kVec; ++k) c[k] = raw_of<R>((D)as_c<S>(c[k]));
+}
+
+template <typename S, bool WIDE, typename R>
+__device__ __forceinline__ void convert_from(int dst_class, R* c) {
+    switch (dst_class) {
+        case CF32: convert_class<S, float>(c); break;
+        case CI32: convert_class<S, int32_t>(c); break;
+        case CU32: convert_class<S, uint32_t>(c); break;
+        default:
+            if constexpr (WIDE) {
+                if (dst_class == CF64) convert_class<S, double>(c);
+                else if (dst_class == CI64) convert_class<S, int64_t>(c);
+                else convert_class<S, uint64_t>(c);
+            }
+            break;
+    }
+}
+
+template <bool WIDE, typename R>
+__device__ __forceinline__ void exec_instr(int op, int arg, R* a, R* b, R* c) {
+    if (op == B200_OP_CONVERT) {
+        const int src = arg >> 4, dst = arg & 15;
+        const int sc = dtype_class(src), dc = dtype_class(dst);
+        if (sc != dc) {
+            switch (sc) {
+                case CF32: convert_from<float, WIDE>(dc, c); break;
+                case CI32: convert_from<int32_t, WIDE>(dc, c); break;
+                case CU32: convert_from<uint32_t, WIDE>(dc, c); break;
+                default:
+                    if constexpr (WIDE) {
+                        if (sc == CF64) convert_from<double, WIDE>(dc, c);
+                        else if (sc == CI64) convert_from<int64_t, WIDE>(dc, c);
+                        else convert_from<uint64_t, WIDE>(dc, c);
+                    }
+                    break;
+            }
+        }
+        if (dtype_is_narrow(dst)) {
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) c[k] = narrow<R>(dst, c[k]);
+        }
+        return;
+    }
+    switch (dtype_class(arg)) {
+        case CF32: exec_class<float>(op, arg, a, b, c); break;
+        case CI32: exec_class<int32_t>(op, arg, a, b, c); break;
+        case CU32: exec_class<uint32_t>(op, arg, a, b, c); break;
+        default:
+            if constexpr (WIDE) {
+                if (dtype_class(arg) == CF64) exec_class<double>(op, arg, a, b, c);
+                else if (dtype_class(arg) == CI64) exec_class<int64_t>(op, arg, a, b, c);
+                else exec_class<uint64_t>(op, arg, a, b, c);
+            }
+            break;
+    }
+}
+
+// Offset of index-space element `lin` inside leaf `L` (general strides / broadcast dims).
+__device__ __forceinline__ int64_t leaf_offset(const ProgramDesc& P, const LeafDesc& L, int64_t lin) {
+    int64_t off = 0;
+    for (int d = 0; d < P.ndim; ++d) {
+        const int64_t e = P.shape[d];
+        const int64_t q = lin / e;
+        off += (lin - q * e) * L.stride[d];
+        lin = q;
+    }
+    return off;
+}
+
+template <typename R>
+__device__ __forceinline__ void fetch_leaf(const ProgramDesc& P, int k, const int64_t lin[kVec], int nvalid, R out[kVec]) {
+    const LeafDesc& L = P.leaves[k];
+    if (L.is_scalar) {
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) out[j] = (R)L.scalar;
+        return;
+    }
+    if (P.linear) {
+        load_vec4<R>(L.ptr, L.dtype, lin[0], P.vec_ok != 0, nvalid, out);
+    } else {
+        const int bytes = dtype_bytes(L.dtype);
+#pragma unroll
+        for (int j = 0; j < kVec; ++j)
+            out[j] = (j < nvalid) ? decode<R>(L.dtype, load_bits(L.ptr, bytes, leaf_offset(P, L, lin[j]))) : (R)0;
+    }
+}
+
+// Evaluates the program for the index-space elements lin[0..nvalid).  In linear mode lin[] must
+// be consecutive and lin[0] a multiple of kVec.
+template <bool WIDE>
+__device__ __forceinline__ void eval_program(const ProgramDesc& P, const int64_t lin[kVec], int nvalid,
+                                             typename RawOf<WIDE>::type result[kVec]) {
+    using R = typename RawOf<WIDE>::type;
+    // Issue the loads of the first array leaves before decoding anything, so that they overlap.
+    R pre[kPrefetch][kVec];
+#pragma unroll
+    for (int k = 0; k < kPrefetch; ++k) {
+        if (k < P.nleaves) fetch_leaf<R>(P, k, lin, nvalid, pre[k]);
+    }
+    // S[0..2] are never-read placeholders below the stack; the stack proper starts at S[3].
+    R S[kMaxStack + 4][kVec];
+    int sp = 0;
+    for (int pc = 0; pc < P.ninstr; ++pc) {
+        const int op = P.code[2 * pc], arg = P.code[2 * pc + 1];
+        if (op == B200_OP_LEAF) {
+#define B200_PUSH(SLOT)                                                            \
+    {                                                                              \
+        switch (arg) {                                                             \
+            case 0: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[0][j]; break; \
+            case 1: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[1][j]; break; \
+            case 2: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[2][j]; break; \
+            case 3: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[3][j]; break; \
+            default: fetch_leaf<R>(P, arg, lin, nvalid, S[SLOT]); break;           \
+        }                                                                          \
+    }
+            switch (sp) {
+                case 0: B200_PUSH(3) break;
+                case 1: B200_PUSH(4) break;
+                case 2: B200_PUSH(5) break;
+                case 3: B200_PUSH(6) break;
+                default: B200_PUSH(7) break;
+            }
+#undef B200_PUSH
+            ++sp;
+        } else {
+            switch (sp) {
+                case 1: exec_instr<WIDE, R>(op, arg, S[0], S[2], S[3]); break;
+                case 2: exec_instr<WIDE, R>(op, arg, S[2], S[3], S[4]); break;
+                case 3: exec_instr<WIDE, R>(op, arg, S[3], S[4], S[5]); break;
+                case 4: exec_instr<WIDE, R>(op, arg, S[4], S[5], S[6]); break;
+                default: exec_instr<WIDE, R>(op, arg, S[5], S[6], S[7]); break;
+            }
+            if (op == B200_OP_MULADD) sp -= 2;
+            else if (op == B200_OP_ADD || op == B200_OP_SUB || op == B200_OP_MUL || op == B200_OP_DIV ||
+                     op == B200_OP_MAX || op == B200_OP_MIN) sp -= 1;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) result[j] = S[3][j];
+}
+
+#endif  // __CUDACC__
+
+}  // namespace b200

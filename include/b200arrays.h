@@ -1,0 +1,248 @@
+/*
+ * b200arrays.h — C ABI of libb200arrays.so: hand-written sm_100a CUDA kernels for the dense
+ * data-parallel array path of AMDGPU.jl (fused broadcast, mapreduce with dims, accumulate,
+ * sort/sortperm) together with the stream-ordered memory pool and the stream/event runtime
+ * those operators sit on.
+ *
+ * Conventions (they follow the reference's FFI layer: gen/hip/generator.jl:44-70 wraps every
+ * driver call in a status check, src/hip/error.jl:143-147 treats "not ready" as a non-error):
+ *   - every function returns an int32 status (B200_OK == 0); b200_last_error() gives the text
+ *     of the calling thread's most recent failure;
+ *   - all array work is asynchronous on the stream handle that is passed in; scalar results are
+ *     written to caller-provided device memory, never returned by value;
+ *   - the library never calls back into the host language and keeps no pointer to caller-owned
+ *     host memory after a call returns (descriptors and programs are consumed before return);
+ *   - the library selects the stream's device itself on every entry, so any host thread may
+ *     call with any handle (this replaces prepare_state, src/tls.jl:192-199);
+ *   - arrays are dense column-major with ELEMENT strides; stride 0 marks a broadcast dimension;
+ *     data pointers only need the natural alignment of their element type;
+ *   - errors found on the device (a bounded wait that ran out) are latched in a per-device
+ *     status word and surface from the next b200_stream_sync / b200_device_sync, the way
+ *     throw_if_exception does (src/runtime/hip-execution.jl:58, src/highlevel.jl:40).
+ */
+#ifndef B200ARRAYS_H
+#define B200ARRAYS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------- */
+enum {
+    B200_OK = 0,
+    B200_NOT_READY = 1,        /* stream/event query: work still in flight (not an error)       */
+    B200_INVALID_ARG = 2,
+    B200_UNSUPPORTED = 3,      /* dtype / op / layout outside the supported set (no CPU fallback)*/
+    B200_OOM = 4,              /* pool or hard limit exhausted; caller may collect and retry    */
+    B200_CUDA_ERROR = 5,
+    B200_NCCL_ERROR = 6,
+    B200_LOOKBACK_TIMEOUT = 7, /* a bounded device-side wait gave up; result is invalid         */
+    B200_NOT_INITIALISED = 8,
+    B200_TOO_LARGE = 9
+};
+
+/* ---- element types ------------------------------------------------------------------------ */
+enum {
+    B200_F16 = 0, B200_BF16 = 1, B200_F32 = 2, B200_F64 = 3,
+    B200_I8 = 4,  B200_I16 = 5,  B200_I32 = 6, B200_I64 = 7,
+    B200_U8 = 8,  B200_U16 = 9,  B200_U32 = 10, B200_U64 = 11,
+    B200_BOOL = 12,
+    B200_DTYPE_COUNT = 13
+};
+
+/* ---- elementwise program opcodes ---------------------------------------------------------- */
+/* A program is a postfix byte string of (opcode, operand) pairs evaluated per output element
+ * on a value stack.  LEAF pushes leaf number `operand`; CONVERT converts the top of stack to
+ * dtype `operand`; every other opcode pops its inputs and pushes one result, computed in dtype
+ * `operand` (inputs must already have that dtype).  16-bit floats compute in binary32 and round
+ * after every operation, small integers wrap to their width, as Julia Base does. */
+enum {
+    B200_OP_LEAF = 0,
+    B200_OP_CONVERT = 1,
+    B200_OP_ADD = 2, B200_OP_SUB = 3, B200_OP_MUL = 4, B200_OP_DIV = 5,
+    B200_OP_MULADD = 6,          /* a*b+c, may be fused (Base.muladd)                           */
+    B200_OP_ABS = 7, B200_OP_ABS2 = 8, B200_OP_EXP = 9,
+    B200_OP_MAX = 10, B200_OP_MIN = 11,   /* NaN-propagating, -0.0 < +0.0 (Base.max/min)        */
+    B200_OP_NEG = 12,
+    B200_OP_COUNT = 13
+};
+
+/* ---- reduction / scan operators ----------------------------------------------------------- */
+enum { B200_RED_ADD = 0, B200_RED_MUL = 1, B200_RED_MAX = 2, B200_RED_MIN = 3, B200_RED_COUNT = 4 };
+
+#define B200_MAX_DIMS 8
+#define B200_MAX_LEAVES 8
+#define B200_MAX_PROGRAM 64      /* instruction pairs */
+
+typedef struct b200_stream_s* b200_stream_t;
+typedef struct b200_event_s*  b200_event_t;
+typedef struct b200_comm_s*   b200_comm_t;
+
+/* Dense array view.  Mirrors what ROCArray hands to a kernel (src/array.jl:19-39: buffer, dims,
+ * byte offset; pointer = base + offset, src/array.jl:353-354). */
+typedef struct {
+    void*   ptr;
+    int32_t dtype;
+    int32_t ndim;
+    int64_t shape[B200_MAX_DIMS];
+    int64_t stride[B200_MAX_DIMS];   /* in elements */
+} b200_tensor;
+
+/* Broadcast leaf: an array or a scalar (Ref / number; src/conversions.jl:1-13). For a scalar,
+ * t.dtype gives the type and `scalar` holds its bits (little-endian, low bytes used). */
+typedef struct {
+    b200_tensor t;
+    int32_t     is_scalar;
+    int32_t     _pad;
+    uint64_t    scalar;
+} b200_leaf;
+
+typedef struct {
+    uint64_t alloc_count, free_count;
+    uint64_t alloc_bytes, free_bytes;     /* cumulative */
+    uint64_t live_bytes, peak_live_bytes; /* library accounting */
+    uint64_t pool_reserved, pool_used;    /* from the CUDA pool attributes */
+    uint64_t hard_limit, soft_limit;
+} b200_pool_stats_t;
+
+typedef struct {
+    char     name[128];
+    int32_t  cc_major, cc_minor, sm_count, l2_bytes_mb;
+    uint64_t total_mem;
+    int32_t  max_smem_per_block, clock_khz;
+} b200_props_t;
+
+/* ---- library / device -------------------------------------------------------------------- */
+/* replaces AMDGPU.__init__ (src/AMDGPU.jl:153-218) */
+int32_t b200_init(void);
+/* replaces HIP.devices / ndevices (src/hip/device.jl:112-124) */
+int32_t b200_device_count(int32_t* n);
+/* replaces HIP.properties / name (src/hip/device.jl:60-110) */
+int32_t b200_device_props(int32_t dev, b200_props_t* out);
+/* replaces HIP.can_access_peer (src/hip/device.jl:147-151) */
+int32_t b200_can_access_peer(int32_t dev, int32_t peer, int32_t* out);
+/* replaces status_message / HIPError text (src/hip/error.jl:1-161) */
+int32_t b200_last_error(char* buf, size_t n);
+const char* b200_status_name(int32_t status);
+/* replaces versioninfo (src/utils.jl:44-90) */
+int32_t b200_version(int32_t* cuda_runtime, int32_t* cuda_driver, int32_t* lib);
+/* replaces AMDGPU.device_synchronize (src/highlevel.jl:63-70) */
+int32_t b200_device_sync(int32_t dev);
+
+/* ---- streams and events ------------------------------------------------------------------ */
+/* replaces HIPStream(priority) (src/hip/stream.jl:4-36); priority in {-1 high, 0 normal, 1 low}
+ * as in the reference (src/hip/stream.jl:17-27) */
+int32_t b200_stream_create(int32_t dev, int32_t priority, b200_stream_t* out);
+/* wraps a cudaStream_t owned by someone else (a torch stream, the legacy stream = NULL) */
+int32_t b200_stream_wrap(int32_t dev, void* cuda_stream, b200_stream_t* out);
+/* replaces the HIPStream finalizer hipStreamDestroy (src/hip/stream.jl:29-33) */
+int32_t b200_stream_destroy(b200_stream_t st);
+/* replaces HIP.synchronize(stream) + throw_if_exception (src/hip/stream.jl:131-143) */
+int32_t b200_stream_sync(b200_stream_t st);
+/* replaces HIP.isdone(stream) (src/hip/stream.jl:45-55): B200_OK or B200_NOT_READY */
+int32_t b200_stream_query(b200_stream_t st);
+int32_t b200_stream_device(b200_stream_t st, int32_t* dev);
+int32_t b200_stream_raw(b200_stream_t st, void** cuda_stream);
+/* replaces HIPEvent (src/hip/event.jl:1-75) */
+int32_t b200_event_create(int32_t dev, int32_t timing, b200_event_t* out);
+int32_t b200_event_destroy(b200_event_t ev);
+int32_t b200_event_record(b200_event_t ev, b200_stream_t st);
+int32_t b200_event_sync(b200_event_t ev);
+int32_t b200_event_query(b200_event_t ev);
+/* replaces HIP.elapsed (src/hip/event.jl:71-75): milliseconds between two recorded events */
+int32_t b200_event_elapsed_ms(b200_event_t start, b200_event_t stop, float* ms);
+/* makes `st` wait for `ev` (replaces HIP.wait(event), src/hip/event.jl:30-36) */
+int32_t b200_stream_wait_event(b200_stream_t st, b200_event_t ev);
+
+/* ---- memory pool --------------------------------------------------------------------------- */
+/* replaces pool_create + hard/soft limits (src/runtime/memory/hip.jl:4-25, src/memory.jl:37-98);
+ * UINT64_MAX = "none" */
+int32_t b200_pool_configure(int32_t dev, uint64_t hard_limit, uint64_t soft_limit);
+/* replaces HIPBuffer(bytes; stream) → hipMallocFromPoolAsync (src/runtime/memory/hip.jl:38-66);
+ * bytes == 0 yields a NULL pointer; B200_OOM is returned (never retried here) so the host can
+ * run the collect-and-retry ladder of alloc_or_retry! (src/runtime/memory/utils.jl:1-47) */
+int32_t b200_malloc_async(void** ptr, size_t bytes, b200_stream_t st);
+/* replaces Mem.free(::HIPBuffer; stream) → hipFreeAsync (src/runtime/memory/hip.jl:82-89) */
+int32_t b200_free_async(void* ptr, b200_stream_t st);
+/* replaces HIP.trim / reclaim (src/hip/pool.jl:36-40, src/memory.jl:333-344) */
+int32_t b200_pool_trim(int32_t dev, size_t keep_bytes);
+/* replaces AllocStats / MemoryStats / pool_status (src/memory.jl:103-166,376-404) */
+int32_t b200_pool_stats(int32_t dev, b200_pool_stats_t* out);
+/* replaces AMDGPU.info / free / total (src/memory.jl:7-35) */
+int32_t b200_mem_info(int32_t dev, size_t* free_bytes, size_t* total_bytes);
+/* replaces Mem.memcpy! (direction inferred; src/runtime/memory/hip.jl:91-102) */
+int32_t b200_memcpy_async(void* dst, const void* src, size_t bytes, b200_stream_t st);
+/* replaces Mem.memset! D8/D16/D32 and fill! (src/runtime/memory/hip.jl:107-117,
+ * src/array.jl:261-266); width_bytes in {1,2,4,8}, count in elements */
+int32_t b200_memset_async(void* dst, uint64_t pattern, int32_t width_bytes, size_t count,
+                          b200_stream_t st);
+/* replaces HostBuffer (pinned) alloc / free (src/runtime/memory/hip.jl:125-192) */
+int32_t b200_host_alloc(void** ptr, size_t bytes);
+int32_t b200_host_free(void* ptr);
+/* replaces Mem.register / unregister (src/runtime/memory/hip.jl:216-267) */
+int32_t b200_host_register(void* ptr, size_t bytes, void** dev_ptr);
+int32_t b200_host_unregister(void* ptr);
+
+/* ---- array operators ----------------------------------------------------------------------- */
+/* replaces the broadcast kernel GPUArrays launches for a Broadcasted{ROCArrayStyle}
+ * (style selection: src/broadcast.jl:3-30): out[I] = program(leaves[I]...) */
+int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, const b200_leaf* leaves,
+                       int32_t nleaves, const uint8_t* program, int32_t ninstr);
+
+/* replaces GPUArrays.mapreducedim!(f, op, R, A; init) (src/kernels/mapreduce.jl:86-173).
+ * The map f (possibly a whole broadcast tree) is given as a program over `leaves`; the index
+ * space is described by `shape` (ndim entries, that of A); R's shape equals it except for
+ * extent 1 in the reduced dimensions.  init == NULL means "R already holds op's neutral
+ * element" (src/kernels/mapreduce.jl:60); otherwise init points to one HOST value of R's dtype
+ * which is folded in exactly once per output.  Empty A leaves R untouched (:91). */
+int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
+                       const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
+                       int32_t ninstr, int32_t op, const void* init);
+
+/* replaces Base.accumulate!(op, B, A; init, dims) → AK.accumulate! (src/kernels/accumulate.jl:1-8).
+ * B and A have equal shape and dtype; dim is 0-based; init is one HOST value of that dtype or
+ * NULL (no seed); inclusive != 0 gives B[i] = op(B[i-1], A[i]) seeded by init. B may alias A. */
+int32_t b200_accumulate(b200_stream_t st, const b200_tensor* B, const b200_tensor* A, int32_t op,
+                        const void* init, int32_t dim, int32_t inclusive);
+
+/* Same scan, seeded by a carry that lives in DEVICE memory (one element of the arrays' type):
+ * the sharded scan passes the fold of the lower ranks' totals without a host round trip.  The
+ * reference has no counterpart (it has no multi-GPU scan). */
+int32_t b200_accumulate_carry(b200_stream_t st, const b200_tensor* B, const b200_tensor* A, int32_t op,
+                              const void* carry_dev, int32_t dim, int32_t inclusive);
+
+/* replaces Base.sort!(x; rev) → AK.sort! (src/kernels/sorting.jl:1): in place, 1-D contiguous,
+ * total order of Base.isless (NaN last, -0.0 < +0.0) */
+int32_t b200_sort(b200_stream_t st, const b200_tensor* x, int32_t rev);
+/* replaces Base.sortperm!(ix, x; rev) → AK.sortperm! (src/kernels/sorting.jl:2-3): ix is Int64,
+ * receives the 1-based stable permutation; x is left untouched */
+int32_t b200_sortperm(b200_stream_t st, const b200_tensor* ix, const b200_tensor* x, int32_t rev);
+
+/* replaces rand!/randn! for the synthetic workloads (src/random.jl:30-70): element i of `out`
+ * becomes gen(seed, stream_id, first_index + i); dist 0: U[0,1), 1: U[-1,1), 2: N(0,1),
+ * 3: integers in [lo,hi], 4: raw low bits.  Counter based, so any slice can be regenerated. */
+int32_t b200_fill_random(b200_stream_t st, const b200_tensor* out, int32_t dist, uint64_t seed,
+                         uint64_t stream_id, uint64_t first_index, int64_t lo, int64_t hi);
+
+/* ---- multi-GPU (one process per GPU) ----------------------------------------------------- */
+/* The reference has no collective layer (multi-GPU is one task per device with host copies,
+ * docs/src/usage/multitasking.md:37-53); these calls are what the sharded operators add. */
+int32_t b200_comm_unique_id(uint8_t id_out[128]);
+int32_t b200_comm_init_rank(b200_comm_t* out, int32_t nranks, int32_t rank,
+                            const uint8_t id[128], int32_t dev);
+int32_t b200_comm_destroy(b200_comm_t comm);
+/* in-place all-reduce of `count` elements of R's dtype on the stream, directly after the kernel
+ * that produced them (no host round trip) */
+int32_t b200_allreduce(b200_comm_t comm, void* buf, size_t count, int32_t dtype, int32_t op,
+                       b200_stream_t st);
+/* gathers `count` elements from every rank into recv[rank*count ...] */
+int32_t b200_allgather(b200_comm_t comm, const void* send, void* recv, size_t count,
+                       int32_t dtype, b200_stream_t st);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ARRAYS_H */
