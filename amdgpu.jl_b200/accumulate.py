@@ -53,3 +53,17 @@ def cumsum(A: ROCArray, dims=None) -> ROCArray:
 def cumprod(A: ROCArray, dims=None) -> ROCArray:
     """``Base.cumprod`` (src/kernels/accumulate.jl:8)."""
     return accumulate_("*", A.similar(), A, init=A.dtype.type(1), dims=dims)
+
+
+def prepared(op, B: ROCArray, A: ROCArray, init=_ZERO, dims: int = 1, stream: Stream | None = None):
+    """``accumulate!`` with the descriptor work done once; returns a zero-argument callable."""
+    if init is _ZERO:
+        init = A.dtype.type(0)
+    init_buf = None if init is None else np.asarray(init, dtype=A.dtype).tobytes()
+    tb, ta = B.tensor(), A.tensor()
+    st = stream or current_stream()
+    fn, opc = lib.b200_accumulate, _op_code(op)
+
+    def launch(_keep=(A, B, st)):
+        check(fn(st.handle, C.byref(tb), C.byref(ta), opc, init_buf, dims - 1, 1))
+    return launch

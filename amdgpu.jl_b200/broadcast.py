@@ -208,6 +208,20 @@ def materialize_(dest: ROCArray, bc, stream: Stream | None = None) -> ROCArray:
     return dest
 
 
+def prepared(dest: ROCArray, bc, stream: Stream | None = None):
+    """Flattens ``dest .= bc`` once and returns a zero-argument callable that re-issues the same
+    launch; for call sites that repeat one expression and want the host cost of a bare C call."""
+    bc = Broadcasted.leaf(bc)
+    code, leaves, nleaves, keep = bc.flatten()
+    t = dest.tensor()
+    st = stream or current_stream()
+    fn, ninstr = lib.b200_broadcast, len(code) // 2
+
+    def launch(_keep=(keep, dest, st)):
+        check(fn(st.handle, C.byref(t), leaves, nleaves, code, ninstr))
+    return launch
+
+
 # dotted-call helpers: bc.exp(x), bc.abs(x), ...
 def exp(x): return Broadcasted.call("exp", x)
 def abs_(x): return Broadcasted.call("abs", x)

@@ -70,6 +70,22 @@ def mapreducedim_(f, op, R: ROCArray, A, init=None, stream: Stream | None = None
     return R
 
 
+def prepared(f, op, R: ROCArray, A, init=None, stream: Stream | None = None):
+    """``mapreducedim!`` with the descriptor work done once; returns a zero-argument callable."""
+    expr = _apply_f(f, A)
+    shape = expr.shape()
+    code, leaves, nleaves, keep = expr.flatten()
+    shp = (C.c_int64 * max(1, len(shape)))(*shape)
+    t = R.tensor()
+    init_buf = None if init is None else np.asarray(init, dtype=R.dtype).tobytes()
+    st = stream or current_stream()
+    fn, ninstr, opc, nd = lib.b200_mapreduce, len(code) // 2, _op_code(op), len(shape)
+
+    def launch(_keep=(keep, R, st)):
+        check(fn(st.handle, C.byref(t), shp, nd, leaves, nleaves, code, ninstr, opc, init_buf))
+    return launch
+
+
 def _result_dtype(expr_dtype: int, opc: int) -> np.dtype:
     # Base.add_sum / mul_prod widen small integers; everything else keeps the mapped type.
     if opc in (_lib.RED_ADD, _lib.RED_MUL):

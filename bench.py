@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""Benchmark of the array hot path on B200.
+
+A step is one pass of the sharded workload over one batch of synthetic input: every GPU holds a
+contiguous shard of 2^30 Float32 elements of x, y, z (U[-1,1), counter-based generator, seed 4)
+and runs  r .= x .* y .+ exp.(-abs.(z))  followed by  sum(abs2, r)  whose one-element partial is
+all-reduced over NCCL on the same stream.  With 8 GPUs that is the 2^33-element configuration;
+per-GPU work is fixed as N grows (weak scaling).  The metric is achieved HBM bandwidth in GB/s:
+algorithmic bytes (16 B/element for the broadcast + 4 B/element for the reduction) over the
+device time of the step, maximum over ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-suite]
+
+For N > 1 launch through torchrun (one rank per GPU); rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+BYTES_PER_ELEM = 16 + 4          # broadcast: 3 reads + 1 write; reduction: 1 read
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()          # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+class Dist:
+    """Host-side plumbing between ranks (gloo): id exchange, barrier, max over ranks."""
+
+    def __init__(self, rank, world):
+        self.rank, self.world, self.dist = rank, world, None
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            import torch.distributed as dist
+            dist.init_process_group("gloo", init_method="env://", rank=rank, world_size=world)
+            self.dist = dist
+
+    def exchange(self, payload):
+        if self.dist is None:
+            return payload
+        box = [payload]
+        self.dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+
+    def max(self, v: float) -> float:
+        if self.dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
+def time_loop(pkg, stream, fn, reps: int) -> float:
+    """Average milliseconds of `fn` over `reps` back-to-back calls, CUDA events on `stream`."""
+    a, b = pkg.Event(stream.device, timing=True), pkg.Event(stream.device, timing=True)
+    stream.synchronize()
+    a.record(stream)
+    for _ in range(reps):
+        fn()
+    b.record(stream)
+    b.synchronize()
+    return pkg.elapsed_ms(a, b) / reps
+
+
+def run_suite(pkg, peak: float) -> dict:
+    """Single-GPU numbers for the other configurations (kernel time, inputs resident in HBM;
+    64 MiB cases rotate over four buffer sets so that they cannot be served from L2)."""
+    R, st = pkg.random, pkg.current_stream()
+    out = {}
+
+    def rec(name, bytes_, ms, extra=None):
+        gbs = bytes_ / ms / 1e6
+        out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_of_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
+                     "frac_of_measured_copy": round(gbs / peak, 3)}
+        if extra:
+            out[name].update(extra)
+
+    # config 1: 2^24 Float32 vectors
+    n = 1 << 24
+    sets = [[R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM01, seed=0, stream_id=4 * s + k) for k in range(2)]
+            + [pkg.ROCArray(np.float32, n)] for s in range(4)]
+    a = np.float32(2.5)
+    i = [0]
+
+    def rotate(calls):
+        def go():
+            calls[i[0] % len(calls)](); i[0] += 1
+        return go
+    # descriptors are prepared once: these kernels run for 10-30 us, a fresh flattening of the
+    # expression in Python for every launch would be timed instead of the kernel
+    rec("c1_axpy_2p24_f32", 12 * n, time_loop(pkg, st, rotate([pkg.broadcast.prepared(z, a * x.dot + y.dot) for x, y, z in sets]), 200))
+    rs = pkg.ROCArray(np.float32, 1)
+    rec("c1_sum_2p24_f32", 4 * n, time_loop(pkg, st, rotate([pkg.mapreduce_prepared("identity", "+", rs, x, init=np.float32(0)) for x, _, _ in sets]), 200))
+    rec("c1_cumsum_2p24_f32", 8 * n, time_loop(pkg, st, rotate([pkg.accumulate_prepared("+", z, x) for x, _, z in sets]), 200))
+    del sets
+    # config 2: 8192 x 8192 matrices
+    m = 8192
+    import ml_dtypes
+    for dt, tag in ((np.float32, "f32"), (np.float16, "f16"), (ml_dtypes.bfloat16, "bf16")):
+        mats = [R.fill_random_(pkg.ROCArray(dt, (m, m)), R.NORMAL, seed=1, stream_id=s) for s in range(2)]
+        r1, r2, r0 = pkg.ROCArray(np.float32, (1, m)), pkg.ROCArray(dt, (m, 1)), pkg.ROCArray(np.float32, (1, 1))
+        zero, ninf = np.float32(0), np.dtype(dt).type(-np.inf)
+        nb = m * m * np.dtype(dt).itemsize
+
+        def d1():
+            A = mats[i[0] % 2]; i[0] += 1
+            pkg.mapreducedim_("identity", "+", r1, A, init=zero)
+
+        def d2():
+            A = mats[i[0] % 2]; i[0] += 1
+            pkg.mapreducedim_("identity", "max", r2, A, init=ninf)
+
+        def sq():
+            A = mats[i[0] % 2]; i[0] += 1
+            pkg.mapreducedim_("abs2", "+", r0, A, init=zero)
+        rec(f"c2_sum_dims1_8192_{tag}", nb, time_loop(pkg, st, d1, 20))
+        rec(f"c2_max_dims2_8192_{tag}", nb, time_loop(pkg, st, d2, 20))
+        rec(f"c2_sumsq_8192_{tag}", nb, time_loop(pkg, st, sq, 20))
+        del mats
+    # config 3: 2^28 scans
+    n = 1 << 28
+    v = R.fill_random_(pkg.ROCArray(np.int32, n), R.INTEGERS, seed=2, lo=-100, hi=100)
+    o = pkg.ROCArray(np.int32, n)
+    rec("c3_scan_2p28_i32", 8 * n, time_loop(pkg, st, lambda: pkg.accumulate_("+", o, v), 10))
+    vf, of = v.reinterpret(np.float32), o.reinterpret(np.float32)
+    R.fill_random_(vf, R.UNIFORM01, seed=2, stream_id=1)
+    rec("c3_scan_2p28_f32", 8 * n, time_loop(pkg, st, lambda: pkg.accumulate_("+", of, vf), 10))
+    # config 4: radix sort (keys are regenerated before every timed sort: it sorts in place)
+    keys = R.fill_random_(v.reinterpret(np.uint32), R.RAWBITS, seed=3)
+    work = o.reinterpret(np.uint32)
+    ts = []
+    for _ in range(5):
+        pkg.copyto_(work, keys)
+        ts.append(time_loop(pkg, st, lambda: pkg.sort_(work), 1))
+    ms = min(ts[1:])
+    out["c4_sort_2p28_u32"] = {"ms": round(ms, 3), "Gkeys/s": round(n / ms / 1e6, 2),
+                               "model_GB/s": round(36 * n / ms / 1e6, 1), "frac_of_8TBs_model36B": round(36 * n / ms / 1e6 / NOMINAL_HBM_GBS, 3)}
+    del keys, work, v, o, vf, of
+    m2 = 1 << 26
+    f = R.fill_random_(pkg.ROCArray(np.float32, m2), R.NORMAL_DUP1PCT, seed=3, hi=m2)
+    ix = pkg.ROCArray(np.int64, m2)
+    pkg.sortperm_(ix, f)
+    ms = min(time_loop(pkg, st, lambda: pkg.sortperm_(ix, f), 1) for _ in range(4))
+    out["c4_sortperm_2p26_f32"] = {"ms": round(ms, 3), "Gkeys/s": round(m2 / ms / 1e6, 2)}
+    return out
+
+
+def cpu_reference_step(n_sample: int, steps: int, warmup: int):
+    """The CPU arm: the same step (fused broadcast, then sum of squares) by the C restatement of
+    Base's loops on all host threads, over a bounded sample of the shard."""
+    orc = entry.load_oracle()
+    from b200_oracle import c_oracle as co   # noqa: E402
+    lib = co.load()
+    threads = lib.ora_max_threads()
+    rng = np.random.default_rng(4)
+    x, y, z = (rng.random(n_sample, dtype=np.float32) * 2 - 1 for _ in range(3))
+    r = np.empty_like(x)
+    px, py, pz, pr = (co.ptr(v, C.c_float) for v in (x, y, z, r))
+
+    def step():
+        lib.ora_muladd_exp_f32(px, py, pz, pr, n_sample, threads)
+        return lib.ora_sum_f32(pr, n_sample, 1, threads)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return dt, threads
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-suite", action="store_true", help="skip the per-configuration kernel numbers")
+    ap.add_argument("--log2-elems", type=int, default=int(os.environ.get("B200_BENCH_LOG2_ELEMS", "30")),
+                    help="log2 of the elements per GPU (30 = the 2^33 / 8-GPU configuration)")
+    args = ap.parse_args()
+    rank, world, local_rank = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")))
+    warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    n = 1 << args.log2_elems
+    workload = (f"config5 shard: r .= x.*y .+ exp.(-abs.(z)); sum(abs2, r) + NCCL allreduce; 2^{args.log2_elems} Float32 "
+                f"elements per GPU (2^33 total at 8 GPUs)")
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        n_sample = 1 << 26
+        dt, threads = cpu_reference_step(n_sample, max(1, args.steps), args.warmup)
+        val = BYTES_PER_ELEM * n_sample / dt / 1e9
+        line = {"impl": "reference", "metric": "achieved HBM GB/s (algorithmic bytes / time), fused broadcast + sum(abs2)",
+                "value": round(val, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": workload, "sample": f"2^26 elements per step on the host ({threads} threads)"},
+                "cpu_baseline": {"value": round(val, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                                 "sample": "2^26-element slice of the shard per step; Julia Base cannot run here, "
+                                           "this is its C restatement with OpenMP over all host threads"},
+                "e2e": {"value": round(val, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+
+    pkg = entry.load_package()
+    if not pkg.functional():
+        raise SystemExit("bench.py needs a CUDA device and the built extension (there is no CPU fallback)")
+    dist = Dist(rank, world)
+    pkg.device_(local_rank)
+    st = pkg.current_stream()
+    comm = None
+    if world > 1:
+        comm = pkg.sharded.init_comm(rank, world, local_rank, dist.exchange)
+    R, bc = pkg.random, pkg.broadcast
+    first = rank * n
+    x, y, z = (R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM11, seed=4, stream_id=s, first_index=first) for s in range(3))
+    r = pkg.ROCArray(np.float32, n)
+    part = pkg.ROCArray(np.float32, 1)
+    zero = np.float32(0)
+    expr = x.dot * y.dot + bc.exp(-bc.abs_(z))
+    launches = [0]
+
+    def step():
+        pkg.materialize_(r, expr)
+        pkg.mapreducedim_("abs2", "+", part, r, init=zero)
+        launches[0] += 2
+        if comm is not None:
+            pkg._lib.check(pkg._lib.lib.b200_allreduce(comm, C.c_void_p(part.ptr), 1, pkg._lib.F32, pkg._lib.RED_ADD, st.handle))
+
+    for _ in range(warmup):
+        step()
+    pkg.device_synchronize()
+    dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches[0] = 0
+    a, b = pkg.Event(timing=True), pkg.Event(timing=True)
+    a.record(st)
+    for _ in range(args.steps):
+        step()
+    b.record(st)
+    b.synchronize()
+    pkg.device_synchronize()
+    dist.barrier()
+    ms_total = dist.max(pkg.elapsed_ms(a, b))
+    timed_launches = launches[0]
+    total_sq = float(part.to_host()[0])
+    ms_step = ms_total / args.steps
+    value = BYTES_PER_ELEM * n * world / ms_step / 1e6
+
+    # ---- kernel-level roofline: the broadcast kernel moves 16 of the 20 bytes per element
+    peak, peak_kind = measured_peak()
+    ms_bc = time_loop(pkg, st, lambda: pkg.materialize_(r, expr), 10)
+    ms_red = time_loop(pkg, st, lambda: pkg.mapreducedim_("abs2", "+", part, r, init=zero), 10)
+    ach = 16 * n / ms_bc / 1e6
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the public API with host buffers
+    ne = min(n, 1 << 28)
+    hbuf = []
+    for k in range(3):
+        p = C.c_void_p()
+        pkg._lib.check(pkg._lib.lib.b200_host_alloc(C.byref(p), 4 * ne))
+        hv = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(ne,))
+        blen = min(ne, 1 << 22)
+        hv.reshape(-1, blen)[:] = R.host_uniform11(4, k, first, blen)
+        hbuf.append((p, hv))
+    hres = C.c_void_p()
+    pkg._lib.check(pkg._lib.lib.b200_host_alloc(C.byref(hres), 4))
+    xe, ye, ze, re_ = (v.view(0, ne) for v in (x, y, z, r))
+    expr_e = xe.dot * ye.dot + bc.exp(-bc.abs_(ze))
+    L = pkg._lib.lib
+
+    def e2e_step():
+        for (p, _), d in zip(hbuf, (xe, ye, ze)):
+            pkg._lib.check(L.b200_memcpy_async(C.c_void_p(d.ptr), p, 4 * ne, st.handle))
+        pkg.materialize_(re_, expr_e)
+        pkg.mapreducedim_("abs2", "+", part, re_, init=zero)
+        if comm is not None:
+            pkg._lib.check(L.b200_allreduce(comm, C.c_void_p(part.ptr), 1, pkg._lib.F32, pkg._lib.RED_ADD, st.handle))
+        pkg._lib.check(L.b200_memcpy_async(hres, C.c_void_p(part.ptr), 4, st.handle))
+        st.synchronize()          # the caller reads the scalar
+    for _ in range(2):
+        e2e_step()
+    dist.barrier()
+    ke = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(ke):
+        e2e_step()
+    e2e_ms = dist.max((time.perf_counter() - t0) * 1e3 / ke)
+    e2e_val = BYTES_PER_ELEM * ne * world / e2e_ms / 1e6
+    for p, _ in hbuf:
+        L.b200_host_free(p)
+    L.b200_host_free(hres)
+
+    suite = None
+    cpu = None
+    if rank == 0 and world == 1:
+        dt, threads = cpu_reference_step(1 << 26, 5, 1)
+        cpu = {"value": round(BYTES_PER_ELEM * (1 << 26) / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": "2^26-element slice of the shard, 5 steps; C restatement of Base's loops with OpenMP on all host threads "
+                         "(Julia Base itself cannot run on this box)"}
+        if not args.no_suite:
+            del x, y, z, r, xe, ye, ze, re_, expr, expr_e
+            suite = run_suite(pkg, peak)
+    dist.barrier()
+    if comm is not None:
+        pkg.sharded.destroy_comm(comm)
+    dist.close()
+    if rank != 0:
+        return
+    line = {
+        "metric": "achieved HBM GB/s (algorithmic bytes / time), fused broadcast + sum(abs2) with allreduce",
+        "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "elements_per_gpu": n, "l2": "inputs (12 GiB per GPU) are far larger than L2",
+                   "frac_of_8TBs_per_gpu": round(value / world / NOMINAL_HBM_GBS, 3), "check_sum_abs2": total_sq},
+        "roofline": {"bound": "hbm", "kernel": "ew_stream_kernel<float, MulAddExpNegAbsF> (r .= x.*y .+ exp.(-abs.(z)))",
+                     "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 3),
+                     "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                     "ms_per_launch": round(ms_bc, 4), "algorithmic_bytes_per_launch": 16 * n,
+                     "reduce_kernel": {"ms_per_launch": round(ms_red, 4), "achieved": round(4 * n / ms_red / 1e6, 1),
+                                       "frac": round(4 * n / ms_red / 1e6 / peak, 3)}},
+        "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": 12 * ne, "d2h_bytes_per_step": 4,
+                "elements_per_gpu": ne, "ms_per_step": round(e2e_ms, 3)},
+        "gpu_launches": timed_launches,
+        "clocks": clocks,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    if suite is not None:
+        line["suite"] = suite
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,86 @@
+"""accumulate! / cumsum / cumprod on the device against the CPU oracle."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from helpers import assert_close, bits_equal
+
+pytestmark = pytest.mark.gpu
+G = np.load(Path(__file__).parent / "golden" / "known_answers.npz")
+NS = (0, 1, 2, 3, 10, 10_000, 16384, 16384 + 1, 4095, 4096, 4097, 8192 * 3 - 1, 1_000_003)
+
+
+def test_golden(gpu):
+    assert bits_equal(gpu.cumsum(gpu.ROCArray.from_host(G["wrap_in"])).to_host(), G["wrap_scan"])
+    assert bits_equal(gpu.cumsum(gpu.ROCArray.from_host(G["pow2_in"])).to_host(), G["pow2_scan"])
+    n = 100_000
+    assert np.array_equal(gpu.cumsum(gpu.ones(np.int64, n)).to_host(), np.arange(1, n + 1))
+    alt = np.where(np.arange(n) % 2 == 0, 1, -1).astype(np.int32)
+    assert np.array_equal(gpu.cumsum(gpu.ROCArray.from_host(alt)).to_host(), (np.arange(n) % 2 == 0).astype(np.int32))
+
+
+@pytest.mark.parametrize("dt", [np.float64, np.float32, np.int32, np.int64, np.float16, np.uint32])
+def test_vector_scans(gpu, orc, dt):
+    dt = np.dtype(dt)
+    rng = np.random.default_rng(0)
+    for n in NS:
+        if dt.itemsize == 2 and n > 20_000:
+            continue                              # prefix sums would leave the Float16 range
+        x = rng.random(n).astype(dt) if dt.kind == "f" else rng.integers(0 if dt.kind == "u" else -100, 101, n).astype(dt)
+        xd = gpu.ROCArray.from_host(x)
+        init = dt.type(rng.random()) if dt.kind == "f" else dt.type(7)
+        for kw, okw in (({}, {}), ({"init": init}, {"init": init})):
+            got = gpu.accumulate("+", xd, **kw).to_host()
+            ref = orc.accumulate("+", x, **okw)
+            assert got.dtype == dt and got.shape == (n,)
+            if dt.kind in "iu":
+                assert np.array_equal(got, ref), (dt, n, kw)
+            else:
+                assert_close(got, ref, {8: 1e-12, 4: 1e-5, 2: 1e-2}[dt.itemsize], (dt, n, kw))
+    # in place, specialised forms, other operators
+    x = (rng.random(50_001) + 0.5).astype(dt) if dt.kind == "f" else rng.integers(1, 3, 50_001).astype(dt)
+    xd = gpu.ROCArray.from_host(x)
+    assert gpu.accumulate_("+", xd, xd) is xd
+    ref = orc.accumulate("+", x)
+    assert np.array_equal(xd.to_host(), ref) if dt.kind in "iu" else np.allclose(xd.to_host(), ref, rtol=1e-2 if dt.itemsize == 2 else 1e-5)
+    y = x[:60]
+    cp = gpu.cumprod(gpu.ROCArray.from_host(y)).to_host()
+    refp = orc.accumulate("*", y)
+    assert np.array_equal(cp, refp) if dt.kind in "iu" else np.allclose(cp.astype(np.float64), refp, rtol=2e-2 if dt.itemsize == 2 else 1e-5)
+    w = rng.standard_normal(70_001).astype(dt) if dt.kind == "f" else rng.integers(0, 1000, 70_001).astype(dt)
+    for op in ("max", "min"):
+        got = gpu.accumulate(op, gpu.ROCArray.from_host(w), init=None).to_host()
+        assert np.array_equal(got.astype(np.float64), orc.accumulate(op, w).astype(np.float64)), (dt, op)
+    # pointer that is not 16-byte aligned
+    v = gpu.ROCArray.from_host(x).view(1, 40_000)
+    got = gpu.cumsum(v).to_host()
+    ref = orc.accumulate("+", x[1:40_000])
+    assert np.array_equal(got, ref) if dt.kind in "iu" else np.allclose(got, ref, rtol=1e-2 if dt.itemsize == 2 else 1e-5)
+
+
+@pytest.mark.parametrize("sizes,dims", [((2,), 2), ((3, 4, 5), 2), ((1, 70, 50, 20), 3), ((3, 100_000), 1),
+                                         ((3, 100_000), 2), ((512, 1000), 1), ((512, 1000), 2), ((10_000, 7), 1),
+                                         ((7, 9000, 3), 2), ((40, 33), 2), ((5000, 40), 2), ((4, 4, 4), 3)])
+def test_multidimensional(gpu, orc, sizes, dims):
+    rng = np.random.default_rng(1)
+    for dt in (np.int64, np.float32):
+        x = rng.integers(-1000, 1000, sizes).astype(dt) if dt == np.int64 else rng.random(sizes).astype(dt)
+        xd = gpu.ROCArray.from_host(x)
+        got = gpu.accumulate("+", xd, dims=dims).to_host()
+        ref = orc.accumulate("+", x, axis=dims - 1) if dims <= x.ndim else x
+        if dt == np.int64:
+            assert np.array_equal(got, ref), (sizes, dims)
+        else:
+            assert_close(got, ref, 1e-5, (sizes, dims))
+    with pytest.raises(ValueError):
+        gpu.accumulate("+", gpu.ROCArray(np.float32, (3, 3)))
+
+
+def test_int32_scan_is_deterministic_and_exact(gpu, orc):
+    rng = np.random.default_rng(2)
+    x = rng.integers(-100, 101, (1 << 22) + 11).astype(np.int32)
+    xd = gpu.ROCArray.from_host(x)
+    outs = [gpu.cumsum(xd).to_host() for _ in range(3)]
+    assert np.array_equal(outs[0], orc.accumulate("+", x))
+    assert all(np.array_equal(outs[0], o) for o in outs[1:])

@@ -1,0 +1,100 @@
+"""Runtime layer on a real device: streams, events, pool accounting, limits, copies, fills."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_and_versions(gpu):
+    p = gpu.device_properties()
+    assert p["cc"][0] == 10 and p["sm_count"] >= 100, p
+    v = gpu.versioninfo()
+    assert v["cuda_runtime"] >= 12000
+    assert gpu.ndevices() >= 1 and gpu.current_device() == 0
+
+
+def test_streams_events_priorities(gpu):
+    for prio in (-1, 0, 1):
+        st = gpu.Stream(0, prio)
+        with gpu.using_stream(st):
+            x = gpu.ROCArray(np.float32, 1 << 20).fill_(1.5)
+            a, b = gpu.Event(timing=True).record(), None
+            y = (x.dot * 2).materialize()
+            b = gpu.Event(timing=True).record()
+            b.synchronize()
+            assert gpu.elapsed_ms(a, b) >= 0.0
+            assert y.to_host()[123] == 3.0
+        st.synchronize()
+        assert st.isdone()
+    with pytest.raises(gpu.B200Error):
+        gpu.Stream(0, 5)
+    with gpu.elapsed() as t:
+        gpu.ROCArray(np.float32, 1 << 22).fill_(0)
+    assert t() > 0
+
+
+def test_copy_fill_views(gpu):
+    rng = np.random.default_rng(0)
+    for dt in (np.uint8, np.int16, np.float16, np.int32, np.float32, np.float64, np.int64):
+        a = (rng.random(1001) * 100).astype(dt)
+        d = gpu.ROCArray.from_host(a)
+        assert np.array_equal(d.to_host(), a)
+        assert np.array_equal(d.copy().to_host(), a)
+        v = d.view(3, 500)                      # pointer not 16-byte aligned
+        assert np.array_equal(v.to_host(), a[3:500])
+        v.fill_(dt(7))
+        a[3:500] = 7
+        assert np.array_equal(d.to_host(), a)
+    m = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    d = gpu.ROCArray.from_host(m)
+    assert np.array_equal(d.to_host(), m)
+    assert np.array_equal(d.reshape(6, 4).to_host(), m.reshape(6, 4, order="F"))
+    assert gpu.zeros(np.int32, (3, 3)).to_host().sum() == 0 and gpu.ones(np.float64, 5).to_host().sum() == 5
+    assert gpu.ROCArray(np.float32, 0).to_host().shape == (0,)
+
+
+def test_pool_accounting_and_limits(gpu):
+    gpu.synchronize()
+    s0 = gpu.pool_stats()
+    x = gpu.ROCArray(np.uint8, 10 << 20)
+    s1 = gpu.pool_stats()
+    assert s1["alloc_count"] == s0["alloc_count"] + 1 and s1["live_bytes"] == s0["live_bytes"] + (10 << 20)
+    x.unsafe_free_()
+    s2 = gpu.pool_stats()
+    assert s2["free_count"] == s0["free_count"] + 1 and s2["live_bytes"] == s0["live_bytes"]
+    with pytest.raises(RuntimeError):
+        x.ptr
+    # out-of-memory injected through the host-side budget: nothing on the GPU faults
+    live = gpu.pool_stats()["live_bytes"]
+    gpu.configure(hard=f"{(live >> 20) + 64} MiB")
+    try:
+        with pytest.raises(gpu.OutOfMemoryError):
+            gpu.ROCArray(np.uint8, 256 << 20)
+        small = gpu.ROCArray(np.uint8, 1 << 20)      # still fine below the limit
+        small.unsafe_free_()
+    finally:
+        gpu.configure(hard="none")
+    big = gpu.ROCArray(np.uint8, 256 << 20)
+    big.unsafe_free_()
+    gpu.synchronize()
+    gpu.reclaim()
+    free, total = gpu.mem_info()
+    assert 0 < free <= total
+
+
+def test_errors_are_reported_not_fatal(gpu):
+    x = gpu.ROCArray.from_host(np.ones(8, np.float32))
+    with pytest.raises(ValueError):
+        gpu.broadcast.Broadcasted.call("sin", x)
+    with pytest.raises(ValueError):
+        gpu.materialize_(gpu.ROCArray(np.float32, 7), x.dot + 1)
+    with pytest.raises(ValueError):
+        gpu.sort_(x, lt=lambda a, b: a > b)
+    bad = gpu._lib.Tensor()
+    bad.dtype, bad.ndim = 99, 1
+    bad.shape[0] = 4
+    import ctypes as C
+    st = gpu._lib.lib.b200_sort(gpu.current_stream().handle, C.byref(bad), 0)
+    assert st == gpu._lib.UNSUPPORTED
+    # the context is still usable afterwards
+    assert float(gpu.sum(x)) == 8.0
