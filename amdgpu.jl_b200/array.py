@@ -45,6 +45,8 @@ class _Managed:
 
 
 class ROCArray:
+    __array_ufunc__ = None      # never let NumPy treat a device array as an object scalar
+
     def __init__(self, dtype, dims, *, _buf: _Managed | None = None, _offset: int = 0, stream: Stream | None = None):
         """``ROCArray{T}(undef, dims)`` (src/array.jl:24-32): uninitialised storage from the pool."""
         self.dtype = np.dtype(dtype)

@@ -67,6 +67,8 @@ class Broadcasted:
     """A node of a lazily fused elementwise expression."""
 
     __slots__ = ("op", "args", "value", "dtype")
+    # NumPy scalars must defer to our reflected operators (np.float32(2.5) * x.dot keeps Float32)
+    __array_ufunc__ = None
 
     def __init__(self, op, args=(), value=None, dtype=None):
         self.op, self.args, self.value, self.dtype = op, args, value, dtype

@@ -3,7 +3,7 @@ import numpy as np
 SIZES = (1, 2, 3, 10, 33, 333, 3333, 4096, 4097, 10_000, 16384, 16385, 100_003, (1 << 20) + 7)
 
 
-def assert_close(got, ref64, rtol, what=""):
+def assert_close(got, ref64, rtol, what="", atol=1e-30):
     got = np.asarray(got, dtype=np.float64)
     ref64 = np.asarray(ref64, dtype=np.float64)
     assert got.shape == ref64.shape, (what, got.shape, ref64.shape)
@@ -11,7 +11,7 @@ def assert_close(got, ref64, rtol, what=""):
     assert nan_ok.all(), (what, "NaN pattern differs")
     m = ~np.isnan(ref64)
     err = np.abs(got[m] - ref64[m])
-    tol = rtol * np.abs(ref64[m]) + 1e-30
+    tol = rtol * np.abs(ref64[m]) + atol
     inf = np.isinf(ref64[m])
     bad = (err > tol) & ~inf
     assert not bad.any(), (what, "max rel err", float((err[~inf] / (np.abs(ref64[m][~inf]) + 1e-300)).max()), "rtol", rtol)

@@ -99,7 +99,8 @@ def test_dims_reductions(gpu, orc, dt):
                 assert np.array_equal(got.astype(np.int64), ref.astype(np.int64)), (dt, shape, dims, f, op)
             else:
                 tol = RTOL[dt] if op == "+" else 0
-                assert_close(got, ref, tol, (dt, shape, dims, f, op))
+                # abs2 of a small Float16 value lands among the Float16 subnormals (quantum 6e-8)
+                assert_close(got, ref, tol, (dt, shape, dims, f, op), atol=1e-7 if dt.itemsize == 2 and f == "abs2" else 1e-30)
 
 
 def test_nan_and_signed_zero(gpu):
