@@ -136,6 +136,20 @@ __device__ __forceinline__ F jl_min(F a, F b) {
     if (a == b) return signbit(a) ? a : b;
     return a < b ? a : b;
 }
+// Binary32 has the same semantics in one instruction: max.NaN / min.NaN return NaN when either
+// input is NaN and order -0.0 below +0.0.
+template <>
+__device__ __forceinline__ float jl_max<float>(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+template <>
+__device__ __forceinline__ float jl_min<float>(float a, float b) {
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
 
 }  // namespace b200
 #endif

@@ -292,7 +292,7 @@ __device__ __forceinline__ void strided_body(const Tin* A, const StridedPlan& pl
         for (int k = 0; k < V; ++k) acc[k] = red_identity<Acc, OP>();
         if (on) {
             const Tin* base = A + k0 + pl.K * (pl.L * m);
-            constexpr int U = 4;
+            constexpr int U = 8;
             int64_t l = lbeg + ty;
             for (; l + (int64_t)(U - 1) * pl.ly < lend; l += (int64_t)U * pl.ly) {
                 VT v[U];
@@ -549,7 +549,7 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
             reduce_contig_thread_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
             return B200_OK;
         }
-        if (M >= target * 2 && (size_t)L * sizeof(Tin) <= 16384) {
+        if (M >= target * 2 && (size_t)L * sizeof(Tin) <= 65536) {
             int64_t blocks = (M + 7) / 8;
             if (blocks > target) blocks = target;
             reduce_contig_warp_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
@@ -580,7 +580,9 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
     pl.K = K; pl.L = L; pl.M = M;
     const int V = vec ? VMAX : 1;
     const int64_t kv = (K + V - 1) / V;
-    pl.kx = (int)(kv < 32 ? kv : 32);
+    // threads along K first: a block covers up to 256 vectors (4 KiB) of every row it touches, so
+    // that DRAM pages are used in long runs; what is left of the block walks different rows
+    pl.kx = (int)(kv < kRedThreads ? kv : kRedThreads);
     pl.ly = kRedThreads / pl.kx;
     if ((int64_t)pl.ly > L) pl.ly = (int)L;
     pl.kblocks = (kv + pl.kx - 1) / pl.kx;

@@ -141,11 +141,20 @@ def time_loop(pkg, stream, fn, reps: int) -> float:
     return pkg.elapsed_ms(a, b) / reps
 
 
-def run_suite(pkg, peak: float) -> dict:
+def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_scale: float = 1.0) -> dict:
     """Single-GPU numbers for the other configurations (kernel time, inputs resident in HBM;
-    64 MiB cases rotate over four buffer sets so that they cannot be served from L2)."""
+    64 MiB cases rotate over four buffer sets so that they cannot be served from L2).
+    `only` selects the cases whose name starts with it; `shrink` divides every size by 2^shrink
+    (small cases for profiler captures)."""
     R, st = pkg.random, pkg.current_stream()
     out = {}
+    i = [0]
+
+    def want(name):
+        return only is None or name.startswith(only)
+
+    def reps(k):
+        return max(1, int(k * reps_scale))
 
     def rec(name, bytes_, ms, extra=None):
         gbs = bytes_ / ms / 1e6
@@ -154,73 +163,74 @@ def run_suite(pkg, peak: float) -> dict:
         if extra:
             out[name].update(extra)
 
-    # config 1: 2^24 Float32 vectors
-    n = 1 << 24
-    sets = [[R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM01, seed=0, stream_id=4 * s + k) for k in range(2)]
-            + [pkg.ROCArray(np.float32, n)] for s in range(4)]
-    a = np.float32(2.5)
-    i = [0]
-
     def rotate(calls):
         def go():
             calls[i[0] % len(calls)](); i[0] += 1
         return go
-    # descriptors are prepared once: these kernels run for 10-30 us, a fresh flattening of the
-    # expression in Python for every launch would be timed instead of the kernel
-    rec("c1_axpy_2p24_f32", 12 * n, time_loop(pkg, st, rotate([pkg.broadcast.prepared(z, a * x.dot + y.dot) for x, y, z in sets]), 200))
-    rs = pkg.ROCArray(np.float32, 1)
-    rec("c1_sum_2p24_f32", 4 * n, time_loop(pkg, st, rotate([pkg.mapreduce_prepared("identity", "+", rs, x, init=np.float32(0)) for x, _, _ in sets]), 200))
-    rec("c1_cumsum_2p24_f32", 8 * n, time_loop(pkg, st, rotate([pkg.accumulate_prepared("+", z, x) for x, _, z in sets]), 200))
-    del sets
+
+    # config 1: 2^24 Float32 vectors.  Descriptors are prepared once: these kernels run for
+    # 10-30 us, a fresh flattening of the expression in Python would be timed instead of them.
+    if want("c1"):
+        n = (1 << 24) >> shrink
+        sets = [[R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM01, seed=0, stream_id=4 * s + k) for k in range(2)]
+                + [pkg.ROCArray(np.float32, n)] for s in range(4)]
+        a = np.float32(2.5)
+        if want("c1_axpy"):
+            rec("c1_axpy_2p24_f32", 12 * n, time_loop(pkg, st, rotate([pkg.broadcast.prepared(z, a * x.dot + y.dot) for x, y, z in sets]), reps(200)))
+        rs = pkg.ROCArray(np.float32, 1)
+        if want("c1_sum"):
+            rec("c1_sum_2p24_f32", 4 * n, time_loop(pkg, st, rotate([pkg.mapreduce_prepared("identity", "+", rs, x, init=np.float32(0)) for x, _, _ in sets]), reps(200)))
+        if want("c1_cumsum"):
+            rec("c1_cumsum_2p24_f32", 8 * n, time_loop(pkg, st, rotate([pkg.accumulate_prepared("+", z, x) for x, _, z in sets]), reps(200)))
+        del sets
     # config 2: 8192 x 8192 matrices
-    m = 8192
-    import ml_dtypes
-    for dt, tag in ((np.float32, "f32"), (np.float16, "f16"), (ml_dtypes.bfloat16, "bf16")):
-        mats = [R.fill_random_(pkg.ROCArray(dt, (m, m)), R.NORMAL, seed=1, stream_id=s) for s in range(2)]
-        r1, r2, r0 = pkg.ROCArray(np.float32, (1, m)), pkg.ROCArray(dt, (m, 1)), pkg.ROCArray(np.float32, (1, 1))
-        zero, ninf = np.float32(0), np.dtype(dt).type(-np.inf)
-        nb = m * m * np.dtype(dt).itemsize
-
-        def d1():
-            A = mats[i[0] % 2]; i[0] += 1
-            pkg.mapreducedim_("identity", "+", r1, A, init=zero)
-
-        def d2():
-            A = mats[i[0] % 2]; i[0] += 1
-            pkg.mapreducedim_("identity", "max", r2, A, init=ninf)
-
-        def sq():
-            A = mats[i[0] % 2]; i[0] += 1
-            pkg.mapreducedim_("abs2", "+", r0, A, init=zero)
-        rec(f"c2_sum_dims1_8192_{tag}", nb, time_loop(pkg, st, d1, 20))
-        rec(f"c2_max_dims2_8192_{tag}", nb, time_loop(pkg, st, d2, 20))
-        rec(f"c2_sumsq_8192_{tag}", nb, time_loop(pkg, st, sq, 20))
-        del mats
+    if want("c2"):
+        m = 8192 >> (shrink // 2)
+        import ml_dtypes
+        for dt, tag in ((np.float32, "f32"), (np.float16, "f16"), (ml_dtypes.bfloat16, "bf16")):
+            if not any(want(f"c2_{k}_8192_{tag}") for k in ("sum_dims1", "max_dims2", "sumsq")):
+                continue
+            mats = [R.fill_random_(pkg.ROCArray(dt, (m, m)), R.NORMAL, seed=1, stream_id=s) for s in range(2)]
+            r1, r2, r0 = pkg.ROCArray(np.float32, (1, m)), pkg.ROCArray(dt, (m, 1)), pkg.ROCArray(np.float32, (1, 1))
+            zero, ninf = np.float32(0), np.dtype(dt).type(-np.inf)
+            nb = m * m * np.dtype(dt).itemsize
+            if want(f"c2_sum_dims1_8192_{tag}"):
+                rec(f"c2_sum_dims1_8192_{tag}", nb, time_loop(pkg, st, rotate([pkg.mapreduce_prepared("identity", "+", r1, A, init=zero) for A in mats]), reps(50)))
+            if want(f"c2_max_dims2_8192_{tag}"):
+                rec(f"c2_max_dims2_8192_{tag}", nb, time_loop(pkg, st, rotate([pkg.mapreduce_prepared("identity", "max", r2, A, init=ninf) for A in mats]), reps(50)))
+            if want(f"c2_sumsq_8192_{tag}"):
+                rec(f"c2_sumsq_8192_{tag}", nb, time_loop(pkg, st, rotate([pkg.mapreduce_prepared("abs2", "+", r0, A, init=zero) for A in mats]), reps(50)))
+            del mats
     # config 3: 2^28 scans
-    n = 1 << 28
-    v = R.fill_random_(pkg.ROCArray(np.int32, n), R.INTEGERS, seed=2, lo=-100, hi=100)
-    o = pkg.ROCArray(np.int32, n)
-    rec("c3_scan_2p28_i32", 8 * n, time_loop(pkg, st, lambda: pkg.accumulate_("+", o, v), 10))
-    vf, of = v.reinterpret(np.float32), o.reinterpret(np.float32)
-    R.fill_random_(vf, R.UNIFORM01, seed=2, stream_id=1)
-    rec("c3_scan_2p28_f32", 8 * n, time_loop(pkg, st, lambda: pkg.accumulate_("+", of, vf), 10))
-    # config 4: radix sort (keys are regenerated before every timed sort: it sorts in place)
-    keys = R.fill_random_(v.reinterpret(np.uint32), R.RAWBITS, seed=3)
-    work = o.reinterpret(np.uint32)
-    ts = []
-    for _ in range(5):
-        pkg.copyto_(work, keys)
-        ts.append(time_loop(pkg, st, lambda: pkg.sort_(work), 1))
-    ms = min(ts[1:])
-    out["c4_sort_2p28_u32"] = {"ms": round(ms, 3), "Gkeys/s": round(n / ms / 1e6, 2),
-                               "model_GB/s": round(36 * n / ms / 1e6, 1), "frac_of_8TBs_model36B": round(36 * n / ms / 1e6 / NOMINAL_HBM_GBS, 3)}
-    del keys, work, v, o, vf, of
-    m2 = 1 << 26
-    f = R.fill_random_(pkg.ROCArray(np.float32, m2), R.NORMAL_DUP1PCT, seed=3, hi=m2)
-    ix = pkg.ROCArray(np.int64, m2)
-    pkg.sortperm_(ix, f)
-    ms = min(time_loop(pkg, st, lambda: pkg.sortperm_(ix, f), 1) for _ in range(4))
-    out["c4_sortperm_2p26_f32"] = {"ms": round(ms, 3), "Gkeys/s": round(m2 / ms / 1e6, 2)}
+    if want("c3") or want("c4_sort"):
+        n = (1 << 28) >> shrink
+        v = R.fill_random_(pkg.ROCArray(np.int32, n), R.INTEGERS, seed=2, lo=-100, hi=100)
+        o = pkg.ROCArray(np.int32, n)
+        if want("c3_scan_2p28_i32"):
+            rec("c3_scan_2p28_i32", 8 * n, time_loop(pkg, st, pkg.accumulate_prepared("+", o, v), reps(10)))
+        if want("c3_scan_2p28_f32"):
+            vf, of = v.reinterpret(np.float32), o.reinterpret(np.float32)
+            R.fill_random_(vf, R.UNIFORM01, seed=2, stream_id=1)
+            rec("c3_scan_2p28_f32", 8 * n, time_loop(pkg, st, pkg.accumulate_prepared("+", of, vf), reps(10)))
+        # config 4: radix sort (keys are copied back before every timed sort: it sorts in place)
+        if want("c4_sort"):
+            keys = R.fill_random_(v.reinterpret(np.uint32), R.RAWBITS, seed=3)
+            work = o.reinterpret(np.uint32)
+            ts = []
+            for _ in range(reps(5) + 1):
+                pkg.copyto_(work, keys)
+                ts.append(time_loop(pkg, st, lambda: pkg.sort_(work), 1))
+            ms = min(ts[1:]) if len(ts) > 1 else ts[0]
+            out["c4_sort_2p28_u32"] = {"ms": round(ms, 3), "Gkeys/s": round(n / ms / 1e6, 2), "model_GB/s": round(36 * n / ms / 1e6, 1),
+                                       "frac_of_8TBs_model36B": round(36 * n / ms / 1e6 / NOMINAL_HBM_GBS, 3)}
+        del v, o
+    if want("c4_sortperm"):
+        m2 = (1 << 26) >> shrink
+        f = R.fill_random_(pkg.ROCArray(np.float32, m2), R.NORMAL_DUP1PCT, seed=3, hi=m2)
+        ix = pkg.ROCArray(np.int64, m2)
+        pkg.sortperm_(ix, f)
+        ms = min(time_loop(pkg, st, lambda: pkg.sortperm_(ix, f), 1) for _ in range(reps(4)))
+        out["c4_sortperm_2p26_f32"] = {"ms": round(ms, 3), "Gkeys/s": round(m2 / ms / 1e6, 2)}
     return out
 
 
@@ -255,6 +265,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-suite", action="store_true", help="skip the per-configuration kernel numbers")
+    ap.add_argument("--case", default=None, help="run only the suite cases whose name starts with this (e.g. c3_scan) and print them")
+    ap.add_argument("--shrink", type=int, default=0, help="with --case: divide the sizes by 2^SHRINK (small cases for profiler captures)")
+    ap.add_argument("--reps-scale", type=float, default=1.0, help="with --case: scale the repetition counts")
     ap.add_argument("--log2-elems", type=int, default=int(os.environ.get("B200_BENCH_LOG2_ELEMS", "30")),
                     help="log2 of the elements per GPU (30 = the 2^33 / 8-GPU configuration)")
     args = ap.parse_args()
@@ -285,6 +298,11 @@ def main():
     pkg = entry.load_package()
     if not pkg.functional():
         raise SystemExit("bench.py needs a CUDA device and the built extension (there is no CPU fallback)")
+    if args.case is not None:
+        pkg.device_(local_rank)
+        print(json.dumps({"case": args.case, "shrink": args.shrink,
+                          "results": run_suite(pkg, measured_peak()[0], args.case, args.shrink, args.reps_scale)}), flush=True)
+        return
     dist = Dist(rank, world)
     pkg.device_(local_rank)
     st = pkg.current_stream()
