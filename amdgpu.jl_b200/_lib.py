@@ -135,6 +135,7 @@ SIGNATURES = {
     "b200_mapreduce": [_vp, _P(Tensor), _P(_i64), _i32, _P(Leaf), _i32, C.c_char_p, _i32, _i32, _vp],
     "b200_accumulate": [_vp, _P(Tensor), _P(Tensor), _i32, _vp, _i32, _i32],
     "b200_accumulate_carry": [_vp, _P(Tensor), _P(Tensor), _i32, _vp, _i32, _i32],
+    "b200_accumulate_noalloc": [_vp, _P(Tensor), _P(Tensor), _i32, _vp, _i32, _i32],
     "b200_sort": [_vp, _P(Tensor), _i32],
     "b200_sortperm": [_vp, _P(Tensor), _P(Tensor), _i32],
     "b200_fill_random": [_vp, _P(Tensor), _i32, _u64, _u64, _u64, _i64, _i64],

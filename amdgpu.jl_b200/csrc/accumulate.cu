@@ -16,6 +16,7 @@
 
 #include <cstring>
 #include <limits>
+#include <mutex>
 #include <type_traits>
 
 namespace b200 {
@@ -368,6 +369,82 @@ static int32_t launch_scan_op(b200_stream_t st, const void* A, void* B, const Sc
     }
 }
 
+
+// ---- scan without any allocation ---------------------------------------------------------------------
+// Some callers may not allocate at all once they are running: a service that handed every byte
+// of device memory to its own arena at start-up, a plug-in whose host forbids driver and pool
+// allocations after initialisation, a control loop with a fixed latency budget that cannot absorb
+// an allocator call.  For them the look-back descriptors and the tile ticket live in this
+// file-scope device array instead of the stream's pool-backed scratch.  Every device that loads the
+// library carries the array (1 MiB) until the process exits.
+constexpr size_t kStaticScanBytes = size_t(1) << 20;
+constexpr size_t kStaticScanHeader = 256;            // ticket word, then the descriptors
+static __device__ __align__(256) unsigned char g_scan_static[kStaticScanBytes];
+
+constexpr int kStaticMaxDevices = 64;
+static std::mutex g_static_mu;
+static void* g_static_addr[kStaticMaxDevices] = {nullptr};
+
+// Device address of g_scan_static on the CURRENT device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use; the real address differs per device
+// and is looked up once per device, with that device current.
+static int32_t static_scan_scratch(int dev, void** out) {
+    if (dev < 0 || dev >= kStaticMaxDevices) return fail(B200_INVALID_ARG, "device %d outside the static-scratch table", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_addr[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_scan_static);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_scan_static)");
+        g_static_addr[dev] = p;
+    }
+    *out = g_static_addr[dev];
+    return B200_OK;
+}
+
+template <typename T, int OP>
+static int32_t launch_scan_static(b200_stream_t st, const void* A, void* B, ScanPlan pl) {
+    using Acc = typename ScanAcc<T>::type;
+    constexpr int V = 16 / sizeof(T);
+    constexpr int TILE = kScanThreads * kScanVecs * V;
+    const int64_t ncols = pl.K * pl.M;
+    const int64_t target = (int64_t)sm_count(st->dev) * 8;
+    const bool thread_cols = (pl.L <= 32 && ncols >= 1024) || (pl.K > 1 && ncols >= 4096);
+    if (thread_cols) {   // this shape needs no scratch at all
+        int64_t blocks = (ncols + 255) / 256;
+        if (blocks > target) blocks = target;
+        scan_column_thread_kernel<T, OP><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
+        return B200_OK;
+    }
+    pl.tiles_per_col = (pl.L + TILE - 1) / TILE;
+    pl.ntiles = pl.tiles_per_col * ncols;
+    const size_t state_bytes = TileState<Acc>::bytes(pl.ntiles);
+    const int64_t max_tiles = (int64_t)((kStaticScanBytes - kStaticScanHeader) / TileState<Acc>::bytes(1));
+    if (pl.ntiles > max_tiles)
+        return fail(B200_TOO_LARGE, "accumulate (no-allocation variant): %lld tiles of %d elements needed, the built-in "
+                    "scratch holds %lld for this element type; use b200_accumulate for larger inputs",
+                    (long long)pl.ntiles, TILE, (long long)max_tiles);
+    void* base = nullptr;
+    B200_TRY(static_scan_scratch(st->dev, &base));
+    const bool aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0 && reinterpret_cast<uintptr_t>(B) % 16 == 0;
+    pl.vec_ok = (pl.K == 1 && aligned && (ncols == 1 || (pl.L * sizeof(T)) % 16 == 0)) ? 1 : 0;
+    // the array keeps whatever the previous call left: ticket and descriptors must start at zero
+    B200_CUDA(cudaMemsetAsync(base, 0, kStaticScanHeader + state_bytes, st->s));
+    scan_lookback_kernel<T, OP><<<(unsigned)pl.ntiles, kScanThreads, 0, st->s>>>(
+        (const T*)A, (T*)B, pl, reinterpret_cast<unsigned char*>(base) + kStaticScanHeader,
+        reinterpret_cast<unsigned int*>(base), device_error_word(st->dev));
+    return B200_OK;
+}
+
+template <typename T>
+static int32_t launch_scan_static_op(b200_stream_t st, const void* A, void* B, const ScanPlan& pl, int op) {
+    switch (op) {
+        case B200_RED_ADD: return launch_scan_static<T, B200_RED_ADD>(st, A, B, pl);
+        case B200_RED_MUL: return launch_scan_static<T, B200_RED_MUL>(st, A, B, pl);
+        case B200_RED_MAX: return launch_scan_static<T, B200_RED_MAX>(st, A, B, pl);
+        default: return launch_scan_static<T, B200_RED_MIN>(st, A, B, pl);
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -433,4 +510,59 @@ extern "C" int32_t b200_accumulate_carry(b200_stream_t st, const b200_tensor* B,
                                          const void* carry_dev, int32_t dim, int32_t inclusive) {
     if (!carry_dev) return fail(B200_INVALID_ARG, "accumulate: null carry pointer");
     return accumulate_common(st, B, A, op, nullptr, carry_dev, dim, inclusive);
+}
+
+// Allocation-free accumulate!: same arguments and results as b200_accumulate, but the scan's
+// bookkeeping lives in a 1 MiB array built into the library, so the call never reaches an
+// allocator (no cudaMalloc, no pool, no stream scratch).  Limits and rules:
+//   * at most 131040 tiles for 4-byte (and 16-bit) element types, 43680 for 8-byte ones; a tile is
+//     4096 four-byte, 2048 eight-byte or 8192 two-byte elements, and every scanned column takes
+//     at least one tile - larger inputs are refused with B200_TOO_LARGE;
+//   * the first call on each device looks up the array's device address; make that call during
+//     start-up, before any stream capture begins;
+//   * all calls on a device share the one array: two calls whose kernels could overlap on the GPU
+//     (different streams without ordering between them) corrupt each other - keep them ordered.
+extern "C" int32_t b200_accumulate_noalloc(b200_stream_t st, const b200_tensor* B, const b200_tensor* A, int32_t op,
+                                           const void* init, int32_t dim, int32_t inclusive) {
+    B200_TRY(enter(st));
+    B200_TRY(check_tensor(B, "accumulate destination"));
+    B200_TRY(check_tensor(A, "accumulate source"));
+    if (op < 0 || op >= B200_RED_COUNT) return fail(B200_UNSUPPORTED, "accumulate: unknown operator %d", op);
+    if (A->dtype != B->dtype) return fail(B200_UNSUPPORTED, "accumulate: source and destination element types differ");
+    if (A->ndim != B->ndim) return fail(B200_INVALID_ARG, "accumulate: source and destination shapes differ");
+    for (int d = 0; d < A->ndim; ++d)
+        if (A->shape[d] != B->shape[d]) return fail(B200_INVALID_ARG, "accumulate: source and destination shapes differ");
+    if (!tensor_is_contiguous(A) || !tensor_is_contiguous(B))
+        return fail(B200_UNSUPPORTED, "accumulate: operands must be dense column-major arrays");
+    if (tensor_numel(A) == 0) return B200_OK;
+    if (dim < 0) return fail(B200_INVALID_ARG, "accumulate: negative dimension");
+    ScanPlan pl{};
+    pl.K = 1; pl.L = 1; pl.M = 1;
+    for (int d = 0; d < A->ndim; ++d) {
+        if (d < dim) pl.K *= A->shape[d];
+        else if (d == dim) pl.L = A->shape[d];
+        else pl.M *= A->shape[d];
+    }
+    pl.inclusive = inclusive ? 1 : 0;
+    pl.has_init = init ? 1 : 0;
+    if (init) {
+        uint64_t bits = 0;
+        memcpy(&bits, init, dtype_size(A->dtype));
+        pl.init = scalar_to_class(A->dtype, bits);
+    }
+    pl.max_polls = 1u << 22;
+    int32_t s;
+    switch (A->dtype) {
+        case B200_F32: s = launch_scan_static_op<float>(st, A->ptr, B->ptr, pl, op); break;
+        case B200_F64: s = launch_scan_static_op<double>(st, A->ptr, B->ptr, pl, op); break;
+        case B200_I32: s = launch_scan_static_op<int32_t>(st, A->ptr, B->ptr, pl, op); break;
+        case B200_I64: s = launch_scan_static_op<int64_t>(st, A->ptr, B->ptr, pl, op); break;
+        case B200_U32: s = launch_scan_static_op<uint32_t>(st, A->ptr, B->ptr, pl, op); break;
+        case B200_U64: s = launch_scan_static_op<uint64_t>(st, A->ptr, B->ptr, pl, op); break;
+        case B200_F16: s = launch_scan_static_op<__half>(st, A->ptr, B->ptr, pl, op); break;
+        case B200_BF16: s = launch_scan_static_op<__nv_bfloat16>(st, A->ptr, B->ptr, pl, op); break;
+        default: return fail(B200_UNSUPPORTED, "accumulate: element type %d is not supported", A->dtype);
+    }
+    B200_TRY(s);
+    return finish(st, "b200_accumulate_noalloc");
 }

@@ -214,6 +214,18 @@ int32_t b200_accumulate(b200_stream_t st, const b200_tensor* B, const b200_tenso
 int32_t b200_accumulate_carry(b200_stream_t st, const b200_tensor* B, const b200_tensor* A, int32_t op,
                               const void* carry_dev, int32_t dim, int32_t inclusive);
 
+/* accumulate! for callers that must not allocate once they are running (a process that gave all
+ * device memory to its own arena, a plug-in whose host forbids allocations after start-up, a
+ * fixed-latency loop).  No counterpart in the reference, which always draws scan temporaries from
+ * its pool.  Same arguments and results as b200_accumulate; the scan's bookkeeping lives in a
+ * 1 MiB array built into the library (held by every device that loads it), so inputs are
+ * limited to 131040 tiles (4096 four-byte / 8192 two-byte elements each) or 43680 tiles of 2048
+ * eight-byte elements, one tile at least per scanned column; beyond that B200_TOO_LARGE.  The
+ * first call on a device resolves the array's address: issue it at start-up, before any stream
+ * capture.  Calls share the array, so calls that could overlap on the GPU must be ordered. */
+int32_t b200_accumulate_noalloc(b200_stream_t st, const b200_tensor* B, const b200_tensor* A,
+                                int32_t op, const void* init, int32_t dim, int32_t inclusive);
+
 /* replaces Base.sort!(x; rev) → AK.sort! (src/kernels/sorting.jl:1): in place, 1-D contiguous,
  * total order of Base.isless (NaN last, -0.0 < +0.0) */
 int32_t b200_sort(b200_stream_t st, const b200_tensor* x, int32_t rev);
