@@ -18,7 +18,9 @@ try:  # bfloat16 host representation
 except Exception:  # pragma: no cover - ml_dtypes ships with the image
     bfloat16 = None
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200arrays.so"
+import os
+
+LIB_PATH = Path(os.environ.get("B200ARRAYS_LIB") or Path(__file__).resolve().parent / "lib" / "libb200arrays.so")
 
 # status codes
 OK, NOT_READY, INVALID_ARG, UNSUPPORTED, OOM, CUDA_ERROR, NCCL_ERROR, LOOKBACK_TIMEOUT, NOT_INITIALISED, TOO_LARGE = range(10)

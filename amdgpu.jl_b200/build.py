@@ -15,7 +15,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
-LIB = HERE / "lib" / "libb200arrays.so"
+LIB = HERE / "lib" / os.environ.get("B200_LIB_NAME", "libb200arrays.so")
+if "B200_LIB_NAME" in os.environ:      # variant builds (tuning experiments) keep their own objects
+    OBJ = HERE / "build" / os.environ["B200_LIB_NAME"].replace(".", "_")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -24,6 +26,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-fmad=false",            # separate multiply/add stay separately rounded (Base semantics)
     "-Xptxas", "-v" if os.environ.get("B200_PTXAS_V") else "-O3",
+    *os.environ.get("B200_EXTRA_NVCC_FLAGS", "").split(),
 ]
 
 
@@ -62,7 +65,7 @@ def _compile_one(src: Path, verbose: bool) -> Path:
 
 
 def build_library(verbose: bool = False, force: bool = False) -> Path:
-    OBJ.mkdir(exist_ok=True)
+    OBJ.mkdir(parents=True, exist_ok=True)
     LIB.parent.mkdir(exist_ok=True)
     if force:
         for f in OBJ.glob("*.stamp"):

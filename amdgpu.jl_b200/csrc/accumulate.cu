@@ -1,19 +1,24 @@
 // accumulate! / cumsum / cumprod: B[i] = op(B[i-1], A[i]) along one dimension.
 //
 // Takes the place of AK.accumulate! as called from src/kernels/accumulate.jl:1-8 of the
-// reference.  The main kernel is a single-pass chained scan with decoupled look-back: every
-// tile of 1024 16-byte vectors is read once and written once (8 bytes per 4-byte element),
-// publishes its aggregate, and resolves its exclusive prefix by inspecting 32 predecessor
-// descriptors at a time.  Tiles take their index from an atomic ticket so that a tile's
-// predecessors are always already running, and every wait is bounded: a tile that runs out of
-// its poll budget latches B200_LOOKBACK_TIMEOUT in the device's error word and leaves; other
-// waiters notice the latched word and leave too.
+// reference.  Three kernels share one descriptor protocol (aggregate / inclusive-prefix words
+// that successors poll):
+//  * long dense vectors: persistent two-pass segment scan (scan_segment_kernel).  A block reduces
+//    a 16-48 KiB segment from HBM, publishes its aggregate, resolves the prefix with one
+//    block-wide look-back, then scans the segment out of L2; both passes are software-pipelined,
+//    HBM sees one read and one write per element (8 bytes per 4-byte element);
+//  * everything else with enough work per column: one tile of 1024 16-byte vectors per block,
+//    chained scan with decoupled look-back, 256 predecessor descriptors per round; tiles take
+//    their index from an atomic ticket so that a tile's predecessors are always running;
+//  * very short columns and wide strided layouts: one thread per column (already coalesced).
+// Every wait is bounded: a block that runs out of its poll budget latches B200_LOOKBACK_TIMEOUT
+// in the device's error word and leaves; other waiters notice the latched word and leave too.
 //
-// The array is collapsed to (K, L, M) around the scanned dimension.  K*M independent columns
-// of L elements (element stride K) run through the same kernel; very short columns and wide
-// strided layouts use one thread per column, which is already coalesced for them.
+// The array is collapsed to (K, L, M) around the scanned dimension: K*M independent columns of
+// L elements with element stride K.
 #include "program.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <mutex>
@@ -151,12 +156,16 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
     __shared__ Acc s_warp[32];
     __shared__ Acc s_wex[32];
     __shared__ Acc s_prefix;
+    __shared__ Acc s_aggregate;
+    __shared__ int s_wflag[kScanWarps];
+    __shared__ int s_verdict;
     __shared__ int s_abort;
 
     TileState<Acc> state;
     state.bind(state_mem, pl.ntiles);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    B200_PHASE_BEGIN();
     if (tid == 0) {
         const unsigned int t = atomicAdd(ticket, 1u);
         if ((int64_t)t == pl.ntiles - 1) *ticket = 0;   // nobody takes a ticket after the last tile
@@ -194,6 +203,7 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
             }
     }
 
+    B200_PHASE_MARK(0);   // ticket + loads issued
     // ---- thread-local inclusive scans per vector, then warp scans of the vector totals
     Acc lane_ex[kScanVecs];
 #pragma unroll
@@ -208,74 +218,95 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
     }
     __syncthreads();
 
-    // ---- warp 0: scan the 32 warp totals, publish, look back
+    B200_PHASE_MARK(1);   // load latency + local scan
+    // ---- warp 0: scan the 32 warp totals; the tile aggregate goes to shared memory
     if (warp == 0) {
         const Acc wt = s_warp[lane];
         const Acc winc = warp_scan_inclusive<Acc, OP>(wt, lane);
         Acc wex = __shfl_up_sync(0xffffffffu, winc, 1);
         if (lane == 0) wex = scan_identity<Acc, OP>();
         s_wex[lane] = wex;
-        const Acc aggregate = __shfl_sync(0xffffffffu, winc, 31);
-
-        Acc prefix = scan_identity<Acc, OP>();
-        bool have_prefix = false;
-        if (jt == 0) {
-            if (pl.has_init) { prefix = scan_seed<T>(pl); have_prefix = true; }
-            if (lane == 0) state.publish(tile, FLAG_PREFIX, have_prefix ? scan_apply<Acc, OP>(prefix, aggregate) : aggregate);
-        } else {
-            if (lane == 0) state.publish(tile, FLAG_AGGREGATE, aggregate);
-            // window of 32 predecessors: lane i inspects tile - 1 - i (of the same column)
-            int64_t look = jt - 1;        // column-local index of the nearest uninspected predecessor
-            bool done = false, abort = false;
-            Acc running = scan_identity<Acc, OP>();
-            bool running_set = false;
-            while (!done && !abort) {
-                const int64_t mine = look - lane;
-                Acc val = scan_identity<Acc, OP>();
-                uint32_t flag = FLAG_PREFIX;     // positions before the column start terminate the walk
-                bool real = mine >= 0;
-                if (real) {
-                    uint32_t polls = 0;
-                    flag = state.peek(col * pl.tiles_per_col + mine, val);
-                    while (flag == FLAG_EMPTY) {
-                        ++polls;
-                        if (polls > pl.max_polls) { abort = true; break; }
-                        if ((polls & 1023u) == 0 && error_latched(err_word)) { abort = true; break; }
-                        if (polls > 32) __nanosleep(polls > 4096 ? 256 : 32);
-                        flag = state.peek(col * pl.tiles_per_col + mine, val);
-                    }
-                }
-                abort = __any_sync(0xffffffffu, abort);
-                if (abort) break;
-                // nearest lane (smallest index) that holds a full prefix ends the walk
-                const uint32_t pmask = __ballot_sync(0xffffffffu, flag == FLAG_PREFIX);
-                const int stop = pmask ? (__ffs(pmask) - 1) : 32;
-                // combine values of lanes 0..stop in tile order (farthest first)
-                Acc contrib = (lane <= stop && (real || lane < stop)) ? val : scan_identity<Acc, OP>();
-                if (!real) contrib = scan_identity<Acc, OP>();
-                // reverse-order inclusive combine: result at lane 0 = v[stop] op ... op v[1] op v[0]
-#pragma unroll
-                for (int off = 1; off < 32; off <<= 1) {
-                    Acc o = __shfl_down_sync(0xffffffffu, contrib, off);
-                    if (lane + off < 32) contrib = scan_apply<Acc, OP>(o, contrib);
-                }
-                const Acc window = __shfl_sync(0xffffffffu, contrib, 0);
-                running = running_set ? scan_apply<Acc, OP>(window, running) : window;
-                running_set = true;
-                if (stop < 32) done = true;
-                else look -= 32;
-            }
-            if (abort) {
-                if (lane == 0) { latch_error(err_word, B200_LOOKBACK_TIMEOUT); s_abort = 1; }
-            } else {
-                prefix = running;
-                have_prefix = true;
-                if (lane == 0) state.publish(tile, FLAG_PREFIX, scan_apply<Acc, OP>(prefix, aggregate));
-            }
-        }
-        if (lane == 0) s_prefix = prefix;
+        if (lane == 31) s_aggregate = winc;
     }
     __syncthreads();
+    const Acc aggregate = s_aggregate;
+
+    // ---- publish, then look back with the WHOLE block: thread t inspects predecessor
+    // look - t, so one round covers 256 tiles.  (A 32-wide window lets the resolved frontier
+    // advance only 32 tiles per L2 round trip, which caps the kernel far below HBM speed once
+    // the first wave of blocks has started in lock step.)
+    if (jt == 0) {
+        if (tid == 0) {
+            Acc prefix = scan_identity<Acc, OP>();
+            if (pl.has_init) prefix = scan_seed<T>(pl);
+            state.publish(tile, FLAG_PREFIX, pl.has_init ? scan_apply<Acc, OP>(prefix, aggregate) : aggregate);
+            s_prefix = prefix;
+        }
+    } else {
+        if (tid == 0) state.publish(tile, FLAG_AGGREGATE, aggregate);
+        int64_t look = jt - 1;            // column-local index of the nearest uninspected predecessor
+        Acc running = scan_identity<Acc, OP>();   // maintained by thread 0
+        bool running_set = false;
+        while (true) {
+            const int64_t mine = look - tid;
+            Acc val = scan_identity<Acc, OP>();
+            uint32_t flag = FLAG_PREFIX;  // positions before the column start terminate the walk
+            const bool real = mine >= 0;
+            bool abort = false;
+            if (real) {
+                uint32_t polls = 0;
+                flag = state.peek(col * pl.tiles_per_col + mine, val);
+                while (flag == FLAG_EMPTY) {
+                    ++polls;
+                    if (polls > pl.max_polls) { abort = true; break; }
+                    if ((polls & 1023u) == 0 && error_latched(err_word)) { abort = true; break; }
+                    if (polls > 32) __nanosleep(polls > 4096 ? 256 : 32);
+                    flag = state.peek(col * pl.tiles_per_col + mine, val);
+                }
+            }
+            abort = __any_sync(0xffffffffu, abort);
+            // inside the warp: the nearest lane holding a full prefix ends the walk; lanes up to it
+            // are combined in tile order (farthest first)
+            const uint32_t pmask = __ballot_sync(0xffffffffu, !abort && flag == FLAG_PREFIX);
+            const int stop = pmask ? (__ffs(pmask) - 1) : 32;
+            Acc contrib = (lane <= stop && real && !abort) ? val : scan_identity<Acc, OP>();
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                Acc o = __shfl_down_sync(0xffffffffu, contrib, off);
+                if (lane + off < 32) contrib = scan_apply<Acc, OP>(o, contrib);
+            }
+            if (lane == 0) {
+                s_warp[warp] = contrib;                       // s_warp is free again at this point
+                s_wflag[warp] = abort ? 2 : (stop < 32 ? 1 : 0);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int verdict = 0;                              // 0: walk on, 1: resolved, 2: give up
+                for (int w = 0; w < kScanWarps; ++w) {        // warp 0 holds the nearest predecessors
+                    if (s_wflag[w] == 2) { verdict = 2; break; }
+                    running = running_set ? scan_apply<Acc, OP>(s_warp[w], running) : s_warp[w];
+                    running_set = true;
+                    if (s_wflag[w] == 1) { verdict = 1; break; }
+                }
+                s_verdict = verdict;
+            }
+            __syncthreads();
+            const int verdict = s_verdict;
+            if (verdict != 0) {
+                if (tid == 0) {
+                    if (verdict == 2) { latch_error(err_word, B200_LOOKBACK_TIMEOUT); s_abort = 1; }
+                    else {
+                        state.publish(tile, FLAG_PREFIX, scan_apply<Acc, OP>(running, aggregate));
+                        s_prefix = running;
+                    }
+                }
+                break;
+            }
+            look -= kScanThreads;
+        }
+    }
+    __syncthreads();
+    B200_PHASE_MARK(2);   // look-back
     if (s_abort) return;
 
     // ---- apply offsets and store
@@ -304,6 +335,301 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
             }
         }
     }
+    B200_PHASE_MARK(3);   // offsets + stores issued
+}
+
+// ---- persistent two-pass scan over L2-sized segments ----------------------------------------------------
+// Long dense vectors.  On this part a dependent descriptor read costs microseconds once the memory
+// pipes are busy, so a look-back per 16 KiB tile cannot be hidden.  Here a block owns whole
+// segments (dealt round-robin over a grid of one resident wave).  Pass 1 streams a segment from
+// HBM and reduces it; the block publishes that aggregate and resolves the segment's prefix with
+// ONE block-wide look-back; pass 2 reads the segment again - it is still in the 126 MB L2, the
+// live segments of all blocks together stay well below that - scans it with the prefix and streams
+// the result out.  The two passes are software-pipelined: while a block scans sub-tile s of its
+// current segment it already reduces sub-tile s of its next one, so HBM reads never pause.  HBM
+// sees one read and one write per element; descriptors and look-backs: one per segment.
+constexpr int kSegThreads = 256;
+constexpr int kSegWarps = kSegThreads / 32;
+constexpr int kSubTileVecs = kSegThreads * kScanVecs;               // 1024 vectors = 16 KiB
+static_assert(kScanVecs * kSegWarps == 32, "warp totals of a sub-tile must fill exactly one warp");
+
+struct SegPlan {
+    int64_t  nvec;           // 16-byte vectors in the whole array
+    int64_t  seg_vecs;       // vectors per segment (a multiple of the sub-tile)
+    int64_t  nsegs;
+    int32_t  inclusive, has_init;
+    uint32_t max_polls;
+    uint64_t init;
+    const void* init_dev;
+};
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kSegThreads, 3)
+scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_word) {
+    using Acc = typename ScanAcc<T>::type;
+    constexpr int V = 16 / sizeof(T);
+    using VT = Vec<T, V>;
+    // per-thread staging of the pass-2 sub-tile: thread t copies and later reads only its own
+    // four vectors, so no barrier guards these buffers, only cp.async group waits
+    __shared__ __align__(16) uint4 s_stage[2][kSubTileVecs];
+    __shared__ Acc s_warp[32];
+    __shared__ Acc s_wex[32];
+    __shared__ Acc s_prefix, s_total;
+    __shared__ int s_wflag[kSegWarps];
+    __shared__ int s_verdict, s_abort;
+
+    TileState<Acc> state;
+    state.bind(state_mem, pl.nsegs);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint4* src = reinterpret_cast<const uint4*>(A);
+    uint4* dst = reinterpret_cast<uint4*>(B);
+    if (tid == 0) s_abort = 0;
+    __syncthreads();
+    B200_PHASE_BEGIN();
+    const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
+
+    // Block-wide reduction of the per-thread pass-1 accumulators and publication of the segment's
+    // aggregate (segment 0 publishes its inclusive prefix at once).  Returns the aggregate.
+    auto publish_aggregate = [&](int64_t seg, Acc* acc) -> Acc {
+        Acc r = acc[0];
+#pragma unroll
+        for (int q = 1; q < V; ++q) r = scan_apply<Acc, OP>(r, acc[q]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) r = scan_apply<Acc, OP>(r, __shfl_down_sync(0xffffffffu, r, o));
+        if (lane == 0) s_warp[warp] = r;
+        __syncthreads();
+        if (warp == 0) {
+            Acc t = lane < kSegWarps ? s_warp[lane] : scan_identity<Acc, OP>();
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t = scan_apply<Acc, OP>(t, __shfl_down_sync(0xffffffffu, t, o));
+            if (lane == 0) {
+                s_total = t;
+                if (seg == 0) {
+                    Acc prefix = scan_identity<Acc, OP>();
+                    if (pl.has_init) prefix = (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
+                    state.publish(0, FLAG_PREFIX, pl.has_init ? scan_apply<Acc, OP>(prefix, t) : t);
+                } else {
+                    state.publish(seg, FLAG_AGGREGATE, t);
+                }
+            }
+        }
+        __syncthreads();
+        const Acc aggregate = s_total;
+        __syncthreads();          // s_total / s_warp may be rewritten right after
+        return aggregate;
+    };
+
+    // ONE block-wide look-back for segment `seg` (thread t inspects segment seg-1-t); leaves the
+    // exclusive prefix in s_prefix and publishes the inclusive one.  False when a wait ran out.
+    auto lookback = [&](int64_t seg, Acc aggregate) -> bool {
+        if (seg == 0) {
+            if (tid == 0) {
+                Acc prefix = scan_identity<Acc, OP>();
+                if (pl.has_init) prefix = (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
+                s_prefix = prefix;
+            }
+            __syncthreads();
+            return true;
+        }
+        int64_t look = seg - 1;
+        Acc running = scan_identity<Acc, OP>();
+        bool running_set = false;
+        while (true) {
+            const int64_t mine = look - tid;
+            Acc val = scan_identity<Acc, OP>();
+            uint32_t flag = FLAG_PREFIX;
+            const bool real = mine >= 0;
+            bool abort = false;
+            if (real) {
+                uint32_t polls = 0;
+                flag = state.peek(mine, val);
+                while (flag == FLAG_EMPTY) {
+                    ++polls;
+                    if (polls > pl.max_polls) { abort = true; break; }
+                    if ((polls & 1023u) == 0 && error_latched(err_word)) { abort = true; break; }
+                    __nanosleep(polls > 64 ? 512 : 128);
+                    flag = state.peek(mine, val);
+                }
+            }
+            abort = __any_sync(0xffffffffu, abort);
+            const uint32_t pmask = __ballot_sync(0xffffffffu, !abort && flag == FLAG_PREFIX);
+            const int stop = pmask ? (__ffs(pmask) - 1) : 32;
+            Acc contrib = (lane <= stop && real && !abort) ? val : scan_identity<Acc, OP>();
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                Acc up = __shfl_down_sync(0xffffffffu, contrib, o);
+                if (lane + o < 32) contrib = scan_apply<Acc, OP>(up, contrib);
+            }
+            if (lane == 0) {
+                s_warp[warp] = contrib;
+                s_wflag[warp] = abort ? 2 : (stop < 32 ? 1 : 0);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int verdict = 0;
+                for (int w = 0; w < kSegWarps; ++w) {
+                    if (s_wflag[w] == 2) { verdict = 2; break; }
+                    running = running_set ? scan_apply<Acc, OP>(s_warp[w], running) : s_warp[w];
+                    running_set = true;
+                    if (s_wflag[w] == 1) { verdict = 1; break; }
+                }
+                s_verdict = verdict;
+                if (verdict == 1) {
+                    state.publish(seg, FLAG_PREFIX, scan_apply<Acc, OP>(running, aggregate));
+                    s_prefix = running;
+                } else if (verdict == 2) {
+                    s_abort = 1;
+                }
+            }
+            __syncthreads();
+            if (s_verdict != 0) break;
+            look -= kSegThreads;
+        }
+        return s_abort == 0;
+    };
+
+    // Pass 1 alone over one segment (prologue only).
+    auto reduce_segment = [&](int64_t seg, Acc* acc) {
+#pragma unroll
+        for (int q = 0; q < V; ++q) acc[q] = scan_identity<Acc, OP>();
+        const int64_t v0 = seg * pl.seg_vecs;
+        const int64_t v1 = (v0 + pl.seg_vecs < pl.nvec) ? v0 + pl.seg_vecs : pl.nvec;
+        for (int64_t base = v0; base < v1; base += kSubTileVecs) {
+            VT v[kScanVecs];
+            bool on[kScanVecs];
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j) {
+                const int64_t vi = base + j * kSegThreads + tid;
+                on[j] = vi < v1;
+                if (on[j]) v[j] = __builtin_bit_cast(VT, ld_policy16(src + vi, keep));
+            }
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j)
+                if (on[j]) {
+#pragma unroll
+                    for (int q = 0; q < V; ++q) acc[q] = scan_apply<Acc, OP>(acc[q], scan_up<T>(v[j].v[q]));
+                }
+        }
+    };
+
+    // ---- prologue: pass 1 of this block's first two segments.  Aggregates are always published
+    // one whole segment before their prefix is needed, so look-backs find them waiting.
+    const int64_t G = gridDim.x;
+    int64_t seg = blockIdx.x;
+    if (seg >= pl.nsegs) return;
+    Acc acc[V];
+    reduce_segment(seg, acc);
+    Acc agg_cur = publish_aggregate(seg, acc);
+    Acc agg_next = scan_identity<Acc, OP>();
+    if (seg + G < pl.nsegs) {
+        reduce_segment(seg + G, acc);
+        agg_next = publish_aggregate(seg + G, acc);
+    }
+    B200_PHASE_MARK(4);   // prologue
+
+    while (true) {
+        if (!lookback(seg, agg_cur)) break;
+        B200_PHASE_MARK(6);   // look-back
+        const int64_t ahead = seg + 2 * G;                 // pass 1 runs two segments ahead
+        const bool has_ahead = ahead < pl.nsegs;
+        const int64_t v0 = seg * pl.seg_vecs;
+        const int64_t v1 = (v0 + pl.seg_vecs < pl.nvec) ? v0 + pl.seg_vecs : pl.nvec;
+        const int64_t n0 = ahead * pl.seg_vecs;
+        const int64_t n1 = has_ahead ? ((n0 + pl.seg_vecs < pl.nvec) ? n0 + pl.seg_vecs : pl.nvec) : n0;
+#pragma unroll
+        for (int q = 0; q < V; ++q) acc[q] = scan_identity<Acc, OP>();
+        Acc carry = s_prefix;
+        bool seeded = (seg != 0) || pl.has_init;
+
+        // stage the first pass-2 sub-tile
+        auto stage = [&](int buf, int64_t sub) {
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j) {
+                const int64_t vi = v0 + sub + j * kSegThreads + tid;
+                if (vi < v1) cp_async16_policy(&s_stage[buf][j * kSegThreads + tid], src + vi, stream);
+            }
+            cp_async_commit();
+        };
+        stage(0, 0);
+        int buf = 0;
+        for (int64_t sub = 0; sub < pl.seg_vecs; sub += kSubTileVecs, buf ^= 1) {
+            if (v0 + sub >= v1 && n0 + sub >= n1) break;
+            // start the copies of the NEXT pass-2 sub-tile (second read of those lines, they come
+            // from L2) and the loads of pass 1 two segments ahead (from HBM, L2 is asked to keep them)
+            stage(buf ^ 1, sub + kSubTileVecs);
+            VT cur[kScanVecs], nxt[kScanVecs];
+            bool non[kScanVecs];
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j) {
+                const int64_t ni = n0 + sub + j * kSegThreads + tid;
+                non[j] = ni < n1;
+                if (non[j]) nxt[j] = __builtin_bit_cast(VT, ld_policy16(src + ni, keep));
+            }
+            cp_async_wait<1>();          // this sub-tile's copies (one younger group may be in flight)
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j) cur[j] = __builtin_bit_cast(VT, s_stage[buf][j * kSegThreads + tid]);
+            // ---- pass 2 on the current sub-tile
+            Acc x[kScanVecs][V];
+            Acc lane_ex[kScanVecs];
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j) {
+                const int64_t vi = v0 + sub + j * kSegThreads + tid;
+#pragma unroll
+                for (int q = 0; q < V; ++q) x[j][q] = (vi < v1) ? scan_up<T>(cur[j].v[q]) : scan_identity<Acc, OP>();
+#pragma unroll
+                for (int q = 1; q < V; ++q) x[j][q] = scan_apply<Acc, OP>(x[j][q - 1], x[j][q]);
+                const Acc inc = warp_scan_inclusive<Acc, OP>(x[j][V - 1], lane);
+                Acc ex = __shfl_up_sync(0xffffffffu, inc, 1);
+                if (lane == 0) ex = scan_identity<Acc, OP>();
+                lane_ex[j] = ex;
+                if (lane == 31) s_warp[j * kSegWarps + warp] = inc;
+            }
+            __syncthreads();
+            if (warp == 0) {
+                const Acc inc = warp_scan_inclusive<Acc, OP>(s_warp[lane], lane);
+                Acc ex = __shfl_up_sync(0xffffffffu, inc, 1);
+                if (lane == 0) ex = scan_identity<Acc, OP>();
+                s_wex[lane] = ex;
+                if (lane == 31) s_total = inc;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j) {
+                const int64_t vi = v0 + sub + j * kSegThreads + tid;
+                Acc o = scan_apply<Acc, OP>(s_wex[j * kSegWarps + warp], lane_ex[j]);
+                if (seeded) o = scan_apply<Acc, OP>(carry, o);
+                VT out;
+                if (pl.inclusive) {
+#pragma unroll
+                    for (int q = 0; q < V; ++q) out.v[q] = scan_down<T>(scan_apply<Acc, OP>(o, x[j][q]));
+                } else {
+                    out.v[0] = scan_down<T>(o);
+#pragma unroll
+                    for (int q = 1; q < V; ++q) out.v[q] = scan_down<T>(scan_apply<Acc, OP>(o, x[j][q - 1]));
+                }
+                if (vi < v1) st_policy16(dst + vi, __builtin_bit_cast(uint4, out), stream);
+            }
+            carry = seeded ? scan_apply<Acc, OP>(carry, s_total) : s_total;
+            seeded = true;
+            // ---- pass 1 on the sub-tile of the segment two ahead
+#pragma unroll
+            for (int j = 0; j < kScanVecs; ++j)
+                if (non[j]) {
+#pragma unroll
+                    for (int q = 0; q < V; ++q) acc[q] = scan_apply<Acc, OP>(acc[q], scan_up<T>(nxt[j].v[q]));
+                }
+            __syncthreads();      // s_warp / s_wex / s_total are reused by the next sub-tile
+        }
+        cp_async_wait<0>();
+        B200_PHASE_MARK(5);   // fused pass 2 (current) + pass 1 (two ahead)
+        Acc agg_ahead = scan_identity<Acc, OP>();
+        if (has_ahead) agg_ahead = publish_aggregate(ahead, acc);
+        seg += G;
+        if (seg >= pl.nsegs) break;
+        agg_cur = agg_next;
+        agg_next = agg_ahead;
+    }
+    if (s_abort && tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
 }
 
 // One thread per column: sequential walk, coalesced across neighbouring columns when K > 1.
@@ -342,10 +668,38 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         scan_column_thread_kernel<T, OP><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
         return B200_OK;
     }
+    const bool aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0 && reinterpret_cast<uintptr_t>(B) % 16 == 0;
+    if (ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {
+        SegPlan sp{};
+        sp.nvec = pl.L * (int64_t)sizeof(T) / 16;
+        int64_t grid = resident_blocks(scan_segment_kernel<T, OP>, kSegThreads, 0, st->dev);
+        // segments: 1..3 sub-tiles of 16 KiB; short vectors get smaller segments so that every
+        // block has work; 48 KiB measured best for long ones (look-backs are rare enough, and
+        // the live segments of all blocks stay far below the L2 capacity)
+        const int64_t subv = kSubTileVecs;
+        const int64_t nsub = (sp.nvec + subv - 1) / subv;
+        int64_t per = nsub / (grid * 3);
+        if (per < 1) per = 1;
+        if (per > 3) per = 3;        // two segments per block are live in L2: 2 x 48 KiB x 444 blocks = 43 MB
+        sp.seg_vecs = per * subv;
+        sp.nsegs = (sp.nvec + sp.seg_vecs - 1) / sp.seg_vecs;
+        sp.inclusive = pl.inclusive;
+        sp.has_init = pl.has_init;
+        sp.max_polls = pl.max_polls;
+        sp.init = pl.init;
+        sp.init_dev = pl.init_dev;
+        void* scr = nullptr;
+        unsigned int* counters = nullptr;
+        const size_t sbytes = TileState<Acc>::bytes(sp.nsegs);
+        B200_TRY(scratch(st, sbytes, &scr, &counters));
+        B200_CUDA(cudaMemsetAsync(scr, 0, sbytes, st->s));
+        if (grid > sp.nsegs) grid = sp.nsegs;
+        scan_segment_kernel<T, OP><<<(unsigned)grid, kSegThreads, 0, st->s>>>((const T*)A, (T*)B, sp, scr, device_error_word(st->dev));
+        return B200_OK;
+    }
     pl.tiles_per_col = (pl.L + TILE - 1) / TILE;
     pl.ntiles = pl.tiles_per_col * ncols;
     if (pl.ntiles >= (int64_t)1 << 31) return fail(B200_TOO_LARGE, "accumulate: too many tiles");
-    const bool aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0 && reinterpret_cast<uintptr_t>(B) % 16 == 0;
     pl.vec_ok = (pl.K == 1 && aligned && (ncols == 1 || (pl.L * sizeof(T)) % 16 == 0)) ? 1 : 0;
     void* scr = nullptr;
     unsigned int* counters = nullptr;
@@ -566,3 +920,5 @@ extern "C" int32_t b200_accumulate_noalloc(b200_stream_t st, const b200_tensor* 
     B200_TRY(s);
     return finish(st, "b200_accumulate_noalloc");
 }
+
+B200_DEFINE_PHASE_READER(b200_debug_phases_scan)

@@ -283,9 +283,8 @@ template <typename T, typename F, int NIN>
 static void launch_stream(b200_stream_t st, void* out, const void* a, const void* b, const void* c, F f, int64_t n) {
     constexpr int V = 16 / sizeof(T);
     const int64_t TILE = (int64_t)kEwThreads * kEwUnroll * V;
-    int64_t tiles = (n + TILE - 1) / TILE;
-    int64_t cap = (int64_t)sm_count(st->dev) * 8;
-    unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    const int64_t tiles = (n + TILE - 1) / TILE;
+    const unsigned grid = balanced_grid(tiles, resident_blocks(ew_stream_kernel<T, F, NIN>, kEwThreads, 0, st->dev));
     auto al = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     int vec_ok = al(out) && al(a) && al(b) && al(c);
     ew_stream_kernel<T, F, NIN><<<grid, kEwThreads, 0, st->s>>>(
@@ -397,10 +396,8 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
     }
 
     const int64_t nvec = (n + kVec - 1) / kVec;
-    int64_t blocks = (nvec + 255) / 256;
-    const int64_t cap = (int64_t)sm_count(st->dev) * 8;
-    if (blocks > cap) blocks = cap;
-    if (C.wide) ew_program_kernel<true><<<(unsigned)blocks, 256, 0, st->s>>>(C.P, O, n);
-    else ew_program_kernel<false><<<(unsigned)blocks, 256, 0, st->s>>>(C.P, O, n);
+    const int64_t chunks = (nvec + 255) / 256;
+    if (C.wide) ew_program_kernel<true><<<balanced_grid(chunks, resident_blocks(ew_program_kernel<true>, 256, 0, st->dev)), 256, 0, st->s>>>(C.P, O, n);
+    else ew_program_kernel<false><<<balanced_grid(chunks, resident_blocks(ew_program_kernel<false>, 256, 0, st->dev)), 256, 0, st->s>>>(C.P, O, n);
     return finish(st, "b200_broadcast");
 }

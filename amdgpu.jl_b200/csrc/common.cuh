@@ -57,6 +57,24 @@ int32_t* device_error_word(int dev);
 int32_t finish(b200_stream_t st, const char* what);
 int sm_count(int dev);
 
+// Blocks of `kernel` that the whole device keeps resident at once (SMs x blocks per SM).
+template <typename Kernel>
+inline int64_t resident_blocks(Kernel kernel, int threads, size_t dyn_smem, int dev) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dyn_smem) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        per_sm = 1;
+    }
+    return (int64_t)per_sm * sm_count(dev);
+}
+// Grid for a block-stride loop over `items` equal work items: every block runs the same number
+// of iterations (up to rounding) and all blocks are resident together - no partly filled wave.
+inline unsigned balanced_grid(int64_t items, int64_t resident) {
+    if (items <= 0) return 1;
+    const int64_t iters = (items + resident - 1) / resident;
+    return (unsigned)((items + iters - 1) / iters);
+}
+
 inline size_t dtype_size(int32_t dt) {
     switch (dt) {
         case B200_F16: case B200_BF16: case B200_I16: case B200_U16: return 2;
@@ -110,6 +128,42 @@ __device__ __forceinline__ void st_stream16(void* p, uint4 v) {
     __stcs(reinterpret_cast<uint4*>(p), v);
 }
 
+// L2 residency control for data that is read twice: the first read asks L2 to keep the lines
+// (evict-last), the second read and all streaming stores mark theirs evict-first.
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint4 ld_policy16(const uint4* ptr, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ void st_policy16(uint4* ptr, uint4 v, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;"
+                 ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(policy) : "memory");
+}
+
+// 16-byte asynchronous copy global -> shared (bypasses registers and L1), grouped by commit/wait.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async16_policy(void* smem_dst, const void* gmem_src, uint64_t policy) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // Records a device-side failure in the device's latched error word (pinned host memory that
 // the host inspects at the next synchronisation).  Spinning kernels poll it on their slow
 // path so that one timed-out wait ends every other wait quickly.
@@ -120,6 +174,35 @@ __device__ __forceinline__ void latch_error(int32_t* word, int32_t code) {
 __device__ __forceinline__ bool error_latched(const int32_t* word) {
     return *(volatile const int32_t*)word != 0;
 }
+
+// Optional phase timing for kernel tuning (compile with -DB200_PHASE_TIMING): thread 0 of a
+// block adds the cycles spent between marks to a global table that b200_debug_phases() returns.
+#ifdef B200_PHASE_TIMING
+static __device__ unsigned long long g_phase_cycles[16];   // one table per translation unit
+#define B200_DEFINE_PHASE_READER(NAME)                                                          \
+    extern "C" int32_t NAME(unsigned long long* out16, int32_t reset) {                         \
+        cudaDeviceSynchronize();                                                                \
+        cudaMemcpyFromSymbol(out16, b200::g_phase_cycles, sizeof(unsigned long long) * 16);     \
+        if (reset) {                                                                            \
+            unsigned long long z[16] = {0};                                                     \
+            cudaMemcpyToSymbol(b200::g_phase_cycles, z, sizeof z);                              \
+        }                                                                                       \
+        return 0;                                                                               \
+    }
+#define B200_PHASE_BEGIN() long long _ph_t = clock64()
+#define B200_PHASE_MARK(i)                                                         \
+    do {                                                                           \
+        if (threadIdx.x == 0) {                                                    \
+            long long _now = clock64();                                            \
+            atomicAdd(&g_phase_cycles[i], (unsigned long long)(_now - _ph_t));     \
+            _ph_t = _now;                                                          \
+        }                                                                          \
+    } while (0)
+#else
+#define B200_DEFINE_PHASE_READER(NAME)
+#define B200_PHASE_BEGIN() do { } while (0)
+#define B200_PHASE_MARK(i) do { } while (0)
+#endif
 
 // Julia Base.max/min on floats: NaN wins, -0.0 orders below +0.0.
 template <typename F>

@@ -17,6 +17,7 @@
 // element plus the outputs.
 #include "program.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <type_traits>
@@ -354,9 +355,17 @@ __device__ __forceinline__ void strided_body(const Tin* A, const StridedPlan& pl
             if (ty == 0 && k0 < pl.K) {
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
+                    // the loads are independent: issue eight at a time, fold them in strip order
                     Acc p = red_identity<Acc, OP>();
-                    for (int s = 0; s < pl.nstrips; ++s)
-                        p = red_apply<Acc, OP>(p, __ldcg(&partials[(tile * pl.nstrips + s) * width + tx * V + k]));
+                    const Acc* src = partials + tile * pl.nstrips * width + tx * V + k;
+                    for (int s0 = 0; s0 < pl.nstrips; s0 += 8) {
+                        Acc t[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            t[j] = (s0 + j < pl.nstrips) ? __ldcg(src + (int64_t)(s0 + j) * width) : red_identity<Acc, OP>();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) p = red_apply<Acc, OP>(p, t[j]);
+                    }
                     finalize<Acc, OP>(out, k0 + k + pl.K * m, p);
                 }
             }
@@ -538,26 +547,24 @@ static uint64_t identity_bits(int redop, int acc_dtype) {
 
 template <typename Tin, typename Acc>
 static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L, int64_t M, int mapop, const RedOut& out) {
-    const int sms = sm_count(st->dev);
-    const int64_t target = (int64_t)sms * 8;
     void* scr = nullptr;
     unsigned int* counters = nullptr;
     if (K == 1) {
         if (M > 1 && L <= 16) {
-            int64_t blocks = (M + kRedThreads - 1) / kRedThreads;
-            if (blocks > target) blocks = target;
-            reduce_contig_thread_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
+            const int64_t res = resident_blocks(reduce_contig_thread_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
+            reduce_contig_thread_kernel<Tin, Acc><<<balanced_grid((M + kRedThreads - 1) / kRedThreads, res), kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
             return B200_OK;
         }
-        if (M >= target * 2 && (size_t)L * sizeof(Tin) <= 65536) {
-            int64_t blocks = (M + 7) / 8;
-            if (blocks > target) blocks = target;
-            reduce_contig_warp_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
+        const int64_t wres = resident_blocks(reduce_contig_warp_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
+        if (M >= wres * 8 && (size_t)L * sizeof(Tin) <= 65536) {
+            reduce_contig_warp_kernel<Tin, Acc><<<balanced_grid((M + 7) / 8, wres), kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
             return B200_OK;
         }
-        // blocks per column: enough to fill the machine, each with at least 64 KiB of input
-        const int64_t min_chunk = (int64_t)(65536 / sizeof(Tin));
-        int64_t B = (target + M - 1) / M;
+        // the grid is exactly one resident wave: blocks per column fill it, each block with at
+        // least 16 KiB of input
+        const int64_t target = resident_blocks(reduce_contig_block_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
+        const int64_t min_chunk = (int64_t)(16384 / sizeof(Tin));
+        int64_t B = target / M;
         const int64_t maxB = (L + min_chunk - 1) / min_chunk;
         if (B > maxB) B = maxB;
         if (B < 1) B = 1;
@@ -567,9 +574,7 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
         chunk = (chunk + grain - 1) / grain * grain;
         B = (L + chunk - 1) / chunk;
         B200_TRY(scratch(st, (size_t)(M * B) * sizeof(Acc), &scr, &counters));
-        int64_t blocks = M * B;
-        if (blocks > target) blocks = target;
-        reduce_contig_block_kernel<Tin, Acc><<<(unsigned)blocks, kRedThreads, 0, st->s>>>(
+        reduce_contig_block_kernel<Tin, Acc><<<balanced_grid(M * B, target), kRedThreads, 0, st->s>>>(
             (const Tin*)A, L, M, (int)B, chunk, mapop, (Acc*)scr, counters, out);
         return B200_OK;
     }
@@ -580,14 +585,16 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
     pl.K = K; pl.L = L; pl.M = M;
     const int V = vec ? VMAX : 1;
     const int64_t kv = (K + V - 1) / V;
-    // threads along K first: a block covers up to 256 vectors (4 KiB) of every row it touches, so
-    // that DRAM pages are used in long runs; what is left of the block walks different rows
-    pl.kx = (int)(kv < kRedThreads ? kv : kRedThreads);
+    // a warp covers 32 vectors (512 B) of a row, the block's other warps take other rows; wider
+    // row chunks measured slower on B200 (fewer column blocks leave more strips to combine)
+    pl.kx = (int)(kv < 32 ? kv : 32);
     pl.ly = kRedThreads / pl.kx;
     if ((int64_t)pl.ly > L) pl.ly = (int)L;
     pl.kblocks = (kv + pl.kx - 1) / pl.kx;
+    const int64_t target = vec ? resident_blocks(reduce_strided_kernel<Tin, Acc, VMAX>, kRedThreads, 0, st->dev)
+                               : resident_blocks(reduce_strided_kernel<Tin, Acc, 1>, kRedThreads, 0, st->dev);
     const int64_t base_blocks = pl.kblocks * M;
-    int64_t ns = (target + base_blocks - 1) / base_blocks;
+    int64_t ns = target / base_blocks;        // strips fill one resident wave
     const int64_t max_ns = (L + (int64_t)pl.ly * 4 - 1) / ((int64_t)pl.ly * 4);
     if (ns > max_ns) ns = max_ns;
     if (ns < 1) ns = 1;
@@ -596,10 +603,9 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
     pl.LS = (pl.LS + pl.ly - 1) / pl.ly * pl.ly;
     pl.nstrips = (int)((L + pl.LS - 1) / pl.LS);
     B200_TRY(scratch(st, (size_t)(base_blocks * pl.nstrips * pl.kx * V) * sizeof(Acc), &scr, &counters));
-    int64_t blocks = base_blocks * pl.nstrips;
-    if (blocks > target * 2) blocks = target * 2;
-    if (vec) reduce_strided_kernel<Tin, Acc, VMAX><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
-    else reduce_strided_kernel<Tin, Acc, 1><<<(unsigned)blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
+    const unsigned blocks = balanced_grid(base_blocks * pl.nstrips, target);
+    if (vec) reduce_strided_kernel<Tin, Acc, VMAX><<<blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
+    else reduce_strided_kernel<Tin, Acc, 1><<<blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
     return B200_OK;
 }
 
@@ -700,8 +706,9 @@ extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const 
     G.acc_dtype = acc_dt;
     G.identity = identity_bits(op, acc_dt);
     if (!G.full) { C.P.linear = 0; C.P.vec_ok = 0; }
-    const int64_t target = (int64_t)sm_count(st->dev) * 8;
-    int64_t B = (target + n_out - 1) / n_out;
+    const int64_t target = C.wide ? resident_blocks(reduce_program_kernel<true>, kRedThreads, 0, st->dev)
+                                  : resident_blocks(reduce_program_kernel<false>, kRedThreads, 0, st->dev);
+    int64_t B = target / n_out;
     const int64_t min_chunk = 16384;
     const int64_t maxB = (n_red + min_chunk - 1) / min_chunk;
     if (B > maxB) B = maxB;
@@ -719,9 +726,8 @@ extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const 
     O.ptr = R->ptr;
     O.dtype = R->dtype;
     for (int d = 0; d < ndim; ++d) O.stride[d] = (d < R->ndim && R->shape[d] != 1) ? R->stride[d] : 0;
-    int64_t blocks = n_out * B;
-    if (blocks > target) blocks = target;
-    if (C.wide) reduce_program_kernel<true><<<(unsigned)blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint64_t*)scr, counters, out);
-    else reduce_program_kernel<false><<<(unsigned)blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint32_t*)scr, counters, out);
+    const unsigned blocks = balanced_grid(n_out * B, target);
+    if (C.wide) reduce_program_kernel<true><<<blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint64_t*)scr, counters, out);
+    else reduce_program_kernel<false><<<blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint32_t*)scr, counters, out);
     return finish(st, "b200_mapreduce");
 }

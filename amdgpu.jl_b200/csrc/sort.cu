@@ -130,6 +130,7 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    B200_PHASE_BEGIN();
     if (tid == 0) {
         const unsigned int t = atomicAdd(a.ticket, 1u);
         if (t == a.ntiles - 1) *a.ticket = 0;
@@ -162,6 +163,7 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         }
     }
 
+    B200_PHASE_MARK(0);   // ticket, histogram clear, loads issued
     // ---- rank inside the warp: keys with equal digits get consecutive ranks in element order
     uint32_t rank[KPT];
     uint32_t* myhist = whist + warp * 256;
@@ -169,7 +171,15 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const uint32_t d = (uint32_t)((key[i] >> a.shift) & 0xff);
-        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        // lanes holding the same digit: eight ballots, one per digit bit (measured far cheaper
+        // on this part than one match.any per key)
+        uint32_t peers = 0xffffffffu;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const bool bit = (d >> b) & 1u;
+            const uint32_t m = __ballot_sync(0xffffffffu, bit);
+            peers &= bit ? m : ~m;
+        }
         const int leader = __ffs(peers) - 1;
         uint32_t base = 0;
         if (lane == leader) {
@@ -181,6 +191,7 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         rank[i] = base + __popc(peers & lt_mask);
     }
     __syncthreads();
+    B200_PHASE_MARK(1);   // load latency + ranking
 
     // ---- per digit: offsets of each warp inside the digit, tile count, publish
     uint32_t c = 0;
@@ -215,6 +226,7 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
     }
     __syncthreads();
 
+    B200_PHASE_MARK(2);   // digit scans, publish
     // ---- keys (and values) to their tile-local sorted position
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
@@ -224,27 +236,43 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         if (PAIRS) vexch[pos] = val[i];
     }
 
+    B200_PHASE_MARK(3);   // exchange scatter
     // ---- decoupled look-back: thread d sums digit d over all earlier tiles
     if (tid < 256) {
         uint32_t excl = 0;
         bool abort = false;
         if (tile > 0) {
+            // kLook predecessors per round: the loads are independent, so one L2 round trip
+            // resolves up to kLook tiles instead of one
+            constexpr int kLook = 8;
             int64_t t = (int64_t)tile - 1;
-            while (true) {
-                const volatile uint32_t* wp = a.state + (size_t)t * 256 + tid;
-                uint32_t w = *wp;
-                uint32_t polls = 0;
-                while ((w >> kFlagShift) == 0) {
-                    ++polls;
-                    if (polls > a.max_polls) { abort = true; break; }
-                    if ((polls & 1023u) == 0 && error_latched(a.err_word)) { abort = true; break; }
-                    if (polls > 32) __nanosleep(polls > 4096 ? 256 : 32);
-                    w = *wp;
+            bool done = false;
+            while (!done && !abort) {
+                uint32_t w[kLook];
+#pragma unroll
+                for (int q = 0; q < kLook; ++q)
+                    w[q] = (t - q >= 0) ? *reinterpret_cast<const volatile uint32_t*>(a.state + (size_t)(t - q) * 256 + tid) : kFlagPrefix;
+#pragma unroll
+                for (int q = 0; q < kLook; ++q) {
+                    if (done || abort) break;
+                    uint32_t v = w[q];
+                    if ((v >> kFlagShift) == 0) {
+                        const volatile uint32_t* wp = a.state + (size_t)(t - q) * 256 + tid;
+                        uint32_t polls = 0;
+                        v = *wp;
+                        while ((v >> kFlagShift) == 0) {
+                            ++polls;
+                            if (polls > a.max_polls) { abort = true; break; }
+                            if ((polls & 1023u) == 0 && error_latched(a.err_word)) { abort = true; break; }
+                            if (polls > 32) __nanosleep(polls > 4096 ? 256 : 32);
+                            v = *wp;
+                        }
+                        if (abort) break;
+                    }
+                    excl += v & kValueMask;
+                    if ((v >> kFlagShift) == 2u) done = true;
                 }
-                if (abort) break;
-                excl += w & kValueMask;
-                if ((w >> kFlagShift) == 2u || t == 0) break;
-                --t;
+                t -= kLook;
             }
             if (!abort)
                 *reinterpret_cast<volatile uint32_t*>(a.state + (size_t)tile * 256 + tid) = kFlagPrefix | (excl + c);
@@ -256,6 +284,7 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         s_goff[tid] = a.bin_base[tid] + excl - s_binstart[tid];
     }
     __syncthreads();
+    B200_PHASE_MARK(4);   // look-back
     if (s_abort) return;
 
     // ---- global scatter, in runs per digit
@@ -274,6 +303,7 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
             }
         }
     }
+    B200_PHASE_MARK(5);   // global scatter issued
 }
 
 template <typename UK> struct SortCfg { static constexpr int KPT = 16; };
@@ -435,3 +465,5 @@ extern "C" int32_t b200_sortperm(b200_stream_t st, const b200_tensor* ix, const 
     if (!ix) return fail(B200_INVALID_ARG, "sortperm!: null index vector");
     return sort_common(st, x, ix, rev, "sortperm!");
 }
+
+B200_DEFINE_PHASE_READER(b200_debug_phases_sort)

@@ -58,7 +58,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -132,6 +132,8 @@ class Dist:
 def time_loop(pkg, stream, fn, reps: int) -> float:
     """Average milliseconds of `fn` over `reps` back-to-back calls, CUDA events on `stream`."""
     a, b = pkg.Event(stream.device, timing=True), pkg.Event(stream.device, timing=True)
+    for _ in range(min(3, reps)):      # untimed: module load, scratch growth, clock ramp
+        fn()
     stream.synchronize()
     a.record(stream)
     for _ in range(reps):
@@ -151,7 +153,7 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
     i = [0]
 
     def want(name):
-        return only is None or name.startswith(only)
+        return only is None or name.startswith(only) or only.startswith(name)
 
     def reps(k):
         return max(1, int(k * reps_scale))
@@ -261,7 +263,7 @@ def cpu_reference_step(n_sample: int, steps: int, warmup: int):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-suite", action="store_true", help="skip the per-configuration kernel numbers")
@@ -325,13 +327,15 @@ def main():
         if comm is not None:
             pkg._lib.check(pkg._lib.lib.b200_allreduce(comm, C.c_void_p(part.ptr), 1, pkg._lib.F32, pkg._lib.RED_ADD, st.handle))
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()            # nvidia-smi needs a moment before its first sample
     for _ in range(warmup):
         step()
     pkg.device_synchronize()
     dist.barrier()
-    sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.lines.clear()      # keep only samples taken while the timed region runs
     launches[0] = 0
     a, b = pkg.Event(timing=True), pkg.Event(timing=True)
     a.record(st)
@@ -342,6 +346,7 @@ def main():
     pkg.device_synchronize()
     dist.barrier()
     ms_total = dist.max(pkg.elapsed_ms(a, b))
+    clocks = sampler.stop() if rank == 0 else None
     timed_launches = launches[0]
     total_sq = float(part.to_host()[0])
     ms_step = ms_total / args.steps
@@ -352,7 +357,6 @@ def main():
     ms_bc = time_loop(pkg, st, lambda: pkg.materialize_(r, expr), 10)
     ms_red = time_loop(pkg, st, lambda: pkg.mapreducedim_("abs2", "+", part, r, init=zero), 10)
     ach = 16 * n / ms_bc / 1e6
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the public API with host buffers
     ne = min(n, 1 << 28)

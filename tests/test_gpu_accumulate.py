@@ -8,7 +8,8 @@ from helpers import assert_close, bits_equal
 
 pytestmark = pytest.mark.gpu
 G = np.load(Path(__file__).parent / "golden" / "known_answers.npz")
-NS = (0, 1, 2, 3, 10, 10_000, 16384, 16384 + 1, 4095, 4096, 4097, 8192 * 3 - 1, 1_000_003)
+NS = (0, 1, 2, 3, 10, 10_000, 16384, 16384 + 1, 4095, 4096, 4097, 8192 * 3 - 1, 1_000_003,
+      1 << 20, (1 << 21) + 32, 3 * (1 << 19) + 4, 5_000_000)     # the last four take the persistent ring kernel
 
 
 def test_golden(gpu):
@@ -84,3 +85,30 @@ def test_int32_scan_is_deterministic_and_exact(gpu, orc):
     outs = [gpu.cumsum(xd).to_host() for _ in range(3)]
     assert np.array_equal(outs[0], orc.accumulate("+", x))
     assert all(np.array_equal(outs[0], o) for o in outs[1:])
+
+
+def test_ring_kernel_small_types_and_variants(gpu, orc):
+    """Long vectors of 16-bit and 64-bit elements, exclusive mode, device-resident carry, max-scan."""
+    n = (1 << 21) + 64
+    alt = np.where(np.arange(n) % 2 == 0, 1.0, -1.0)
+    for dt in (np.float16, np.int64, np.float64):
+        x = alt.astype(dt)
+        got = gpu.cumsum(gpu.ROCArray.from_host(x)).to_host()
+        assert np.array_equal(got, (np.arange(n) % 2 == 0).astype(dt)), dt
+    rng = np.random.default_rng(5)
+    x = rng.integers(-100, 101, n).astype(np.int32)
+    xd = gpu.ROCArray.from_host(x)
+    ex = gpu.accumulate_("+", gpu.ROCArray(np.int32, n), xd, init=np.int32(11), inclusive=False).to_host()
+    ref = orc.accumulate("+", x, init=np.int32(11))
+    assert ex[0] == 11 and np.array_equal(ex[1:], ref[:-1])
+    w = rng.standard_normal(n).astype(np.float32)
+    assert np.array_equal(gpu.accumulate("max", gpu.ROCArray.from_host(w), init=None).to_host(), np.maximum.accumulate(w))
+    # carry in device memory (the sharded scan's second phase)
+    import ctypes as C
+    L = gpu._lib
+    carry = gpu.ROCArray.from_host(np.array([1000], dtype=np.int32))
+    out = gpu.ROCArray(np.int32, n)
+    tb, ta = out.tensor(), xd.tensor()
+    assert L.lib.b200_accumulate_carry(gpu.current_stream().handle, C.byref(tb), C.byref(ta), L.RED_ADD,
+                                       C.c_void_p(carry.ptr), 0, 1) == L.OK
+    assert np.array_equal(out.to_host(), orc.accumulate("+", x, init=np.int32(1000)))
