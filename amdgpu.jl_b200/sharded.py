@@ -64,9 +64,10 @@ class ShardedOps:
 class DeviceBackend:
     """Library kernels + NCCL through the C ABI."""
 
-    def __init__(self, comm, stream=None):
+    def __init__(self, comm, world_size: int, stream=None):
         from .runtime import current_stream
         self.comm = comm
+        self.world_size = world_size
         self.stream = stream or current_stream()
 
     def local_mapreduce(self, f, op, shard):
@@ -98,8 +99,6 @@ class DeviceBackend:
         check(lib.b200_allgather(self.comm, C.c_void_p(holder.ptr), C.c_void_p(out.ptr), holder.size,
                                  _lib.dtype_code(holder.dtype), self.stream.handle))
         return out
-
-    world_size = 1
 
     def fold_prefix(self, op, totals, rank):
         return self.local_mapreduce(None, op, totals.view(0, rank))

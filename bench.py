@@ -33,6 +33,10 @@ sys.path.insert(0, str(ROOT))
 import __graft_entry__ as entry  # noqa: E402
 
 BYTES_PER_ELEM = 16 + 4          # broadcast: 3 reads + 1 write; reduction: 1 read
+# DRAM bytes per element of the broadcast kernel from its ncu capture on a 2^26-element shard
+# (dram__bytes_read.sum + dram__bytes_write.sum = 1041.0 MB for 2^26 elements); traffic grows in
+# proportion to the element count, so a launch over n elements moves this many bytes per element.
+EW_TRAFFIC_BYTES_PER_ELEM = 1041.0e6 / (1 << 26)
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -421,7 +425,8 @@ def main():
                    "frac_of_8TBs_per_gpu": round(value / world / NOMINAL_HBM_GBS, 3), "check_sum_abs2": total_sq},
         "roofline": {"bound": "hbm", "kernel": "ew_stream_kernel<float, MulAddExpNegAbsF> (r .= x.*y .+ exp.(-abs.(z)))",
                      "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 3),
-                     "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                     "peak_source": f"{peak_kind} copy bandwidth", "traffic": round(EW_TRAFFIC_BYTES_PER_ELEM * n),
+                     "traffic_source": "ncu capture at 2^26 elements scaled by the element count",
                      "ms_per_launch": round(ms_bc, 4), "algorithmic_bytes_per_launch": 16 * n,
                      "reduce_kernel": {"ms_per_launch": round(ms_red, 4), "achieved": round(4 * n / ms_red / 1e6, 1),
                                        "frac": round(4 * n / ms_red / 1e6 / peak, 3)}},
