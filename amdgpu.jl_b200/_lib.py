@@ -141,6 +141,10 @@ SIGNATURES = {
     "b200_sort": [_vp, _P(Tensor), _i32],
     "b200_sortperm": [_vp, _P(Tensor), _P(Tensor), _i32],
     "b200_fill_random": [_vp, _P(Tensor), _i32, _u64, _u64, _u64, _i64, _i64],
+    "b200_peer_create": [_i32, _i32, _i32, _P(_vp), C.c_char_p],
+    "b200_peer_connect": [_vp, C.c_char_p],
+    "b200_peer_destroy": [_vp],
+    "b200_mapreduce_allreduce": [_vp, _vp, _P(Tensor), _P(_i64), _i32, _P(Leaf), _i32, C.c_char_p, _i32, _i32, _vp],
     "b200_comm_unique_id": [C.c_char_p],
     "b200_comm_init_rank": [_P(_vp), _i32, _i32, C.c_char_p, _i32],
     "b200_comm_destroy": [_vp],

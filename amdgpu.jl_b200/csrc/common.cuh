@@ -26,6 +26,23 @@ struct b200_event_s {
     cudaEvent_t e;
 };
 
+// Peer exchange for fused reduce + all-reduce (one process per GPU): every rank owns a small
+// buffer of slots that all ranks can write over NVLink; `bufs[r]` is rank r's buffer as mapped
+// into THIS process (own buffer for r == rank).
+constexpr int kMaxPeers = 8;
+struct PeerSlot {
+    unsigned long long value;    // accumulator bits
+    unsigned long long seq;      // sequence number of the collective that wrote `value`
+};
+struct PeerCtx {
+    int32_t   nranks;            // 0: no exchange, plain local result
+    int32_t   rank;
+    uint64_t  seq;               // this collective's number (1, 2, ...); parity selects the slot bank
+    uint32_t  max_polls;
+    int32_t*  err_word;
+    PeerSlot* bufs[kMaxPeers];   // each: [2 banks][kMaxPeers] slots
+};
+
 namespace b200 {
 
 // Thread-local error text; returns `code` so call sites can `return fail(...)`.
@@ -103,6 +120,8 @@ inline bool tensor_is_contiguous(const b200_tensor* t) {
     return true;
 }
 int32_t check_tensor(const b200_tensor* t, const char* name);
+// Fills the kernel-side view of a peer group for its next collective (advances the sequence).
+int32_t peer_next_context(b200_peer_t peer, b200_stream_t st, PeerCtx* out);
 
 }  // namespace b200
 

@@ -146,6 +146,60 @@ __device__ __forceinline__ void finalize(const RedOut& o, int64_t idx, Acc v) {
     store_result<Acc>(o.R, o.rdtype, idx, red_apply<Acc, OP>(seed, v));
 }
 
+// Final step of a full reduction.  Without peers: thread 0 stores op(seed, v).  With peers (the
+// fused reduce + all-reduce): the block stores this rank's partial into every rank's exchange
+// slot over NVLink, waits (bounded) until the partials of all ranks have arrived in its own
+// buffer and folds them in rank order, so every rank obtains the same bits.  `v` is valid in
+// thread 0; all threads of the block must call.
+template <typename Acc, int OP>
+__device__ __forceinline__ void block_finalize(const RedOut& o, const PeerCtx& peer, int64_t idx, Acc v) {
+    if (peer.nranks == 0) {
+        if (threadIdx.x == 0) finalize<Acc, OP>(o, idx, v);
+        return;
+    }
+    __shared__ unsigned long long s_bits[kMaxPeers];
+    __shared__ int s_peer_abort;
+    const int tid = threadIdx.x;
+    const int bank = (int)(peer.seq & 1ull) * kMaxPeers;
+    if (tid == 0) { s_bits[0] = raw_of<uint64_t>(v); s_peer_abort = 0; }
+    __syncthreads();
+    const unsigned long long mine = s_bits[0];
+    __syncthreads();
+    if (tid < peer.nranks) {
+        // my partial -> slot [bank][rank] of rank `tid` (a peer store unless tid == rank)
+        volatile PeerSlot* dst = peer.bufs[tid] + bank + peer.rank;
+        dst->value = mine;
+        __threadfence_system();
+        dst->seq = peer.seq;
+        // rank tid's partial <- my own buffer
+        volatile PeerSlot* src = peer.bufs[peer.rank] + bank + tid;
+        uint32_t polls = 0;
+        bool ok = true;
+        while (src->seq != peer.seq) {
+            if (++polls > peer.max_polls) { ok = false; break; }
+            if ((polls & 1023u) == 0 && error_latched(peer.err_word)) { ok = false; break; }
+            __nanosleep(polls > 256 ? 256 : 32);
+        }
+        if (ok) {
+            __threadfence_system();
+            s_bits[tid] = src->value;
+        } else {
+            s_peer_abort = 1;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (s_peer_abort) {
+            latch_error(peer.err_word, B200_LOOKBACK_TIMEOUT);
+        } else {
+            Acc total = as_c<Acc, uint64_t>(s_bits[0]);
+            for (int r = 1; r < peer.nranks; ++r) total = red_apply<Acc, OP>(total, as_c<Acc, uint64_t>(s_bits[r]));
+            finalize<Acc, OP>(o, idx, total);
+        }
+    }
+    __syncthreads();
+}
+
 // (map, op) pairs with a statically specialised inner loop; everything else uses the evaluator.
 #define B200_MAPOP(MAPV, OPV) ((MAPV) * 4 + (OPV))
 #define B200_MAPOP_SWITCH(mapop, CALL)                                                             \
@@ -171,7 +225,8 @@ static bool mapop_supported(int map, int op) {
 // folds the B partials.
 template <typename Tin, typename Acc, int MAP, int OP>
 __device__ __forceinline__ void contig_block_body(const Tin* A, int64_t L, int64_t M, int B, int64_t chunk,
-                                                  Acc* partials, unsigned int* counters, const RedOut& out) {
+                                                  Acc* partials, unsigned int* counters, const RedOut& out,
+                                                  const PeerCtx& peer) {
     constexpr int V = 16 / sizeof(Tin);
     __shared__ Acc smem[32];
     __shared__ int s_last;
@@ -188,7 +243,7 @@ __device__ __forceinline__ void contig_block_body(const Tin* A, int64_t L, int64
         if (end > beg) segment_accumulate<Tin, Acc, MAP, OP, V>(A + m * L + beg, end - beg, threadIdx.x, blockDim.x, acc);
         Acc v = block_reduce<Acc, OP>(fold_lanes<Acc, OP, V>(acc), smem);
         if (B == 1) {
-            if (threadIdx.x == 0) finalize<Acc, OP>(out, m, v);
+            block_finalize<Acc, OP>(out, peer, m, v);
             continue;
         }
         if (threadIdx.x == 0) {
@@ -204,7 +259,7 @@ __device__ __forceinline__ void contig_block_body(const Tin* A, int64_t L, int64
             Acc p = red_identity<Acc, OP>();
             for (int j = threadIdx.x; j < B; j += blockDim.x) p = red_apply<Acc, OP>(p, __ldcg(&partials[m * B + j]));
             p = block_reduce<Acc, OP>(p, smem);
-            if (threadIdx.x == 0) finalize<Acc, OP>(out, m, p);
+            block_finalize<Acc, OP>(out, peer, m, p);
         }
         __syncthreads();
     }
@@ -213,8 +268,8 @@ __device__ __forceinline__ void contig_block_body(const Tin* A, int64_t L, int64
 template <typename Tin, typename Acc>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_contig_block_kernel(const Tin* A, int64_t L, int64_t M, int B, int64_t chunk, int mapop,
-                           Acc* partials, unsigned int* counters, RedOut out) {
-#define CALL(MAPV, OPV) contig_block_body<Tin, Acc, MAPV, OPV>(A, L, M, B, chunk, partials, counters, out)
+                           Acc* partials, unsigned int* counters, RedOut out, const __grid_constant__ PeerCtx peer) {
+#define CALL(MAPV, OPV) contig_block_body<Tin, Acc, MAPV, OPV>(A, L, M, B, chunk, partials, counters, out, peer)
     B200_MAPOP_SWITCH(mapop, CALL)
 #undef CALL
 }
@@ -546,17 +601,23 @@ static uint64_t identity_bits(int redop, int acc_dtype) {
 }
 
 template <typename Tin, typename Acc>
-static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L, int64_t M, int mapop, const RedOut& out) {
+static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L, int64_t M, int mapop, const RedOut& out,
+                           const PeerCtx* peer = nullptr) {
     void* scr = nullptr;
     unsigned int* counters = nullptr;
+    PeerCtx pc{};
+    if (peer) {
+        if (K != 1 || M != 1) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce handles full reductions only");
+        pc = *peer;
+    }
     if (K == 1) {
-        if (M > 1 && L <= 16) {
+        if (!peer && M > 1 && L <= 16) {
             const int64_t res = resident_blocks(reduce_contig_thread_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
             reduce_contig_thread_kernel<Tin, Acc><<<balanced_grid((M + kRedThreads - 1) / kRedThreads, res), kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
             return B200_OK;
         }
         const int64_t wres = resident_blocks(reduce_contig_warp_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
-        if (M >= wres * 8 && (size_t)L * sizeof(Tin) <= 65536) {
+        if (!peer && M >= wres * 8 && (size_t)L * sizeof(Tin) <= 65536) {
             reduce_contig_warp_kernel<Tin, Acc><<<balanced_grid((M + 7) / 8, wres), kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
             return B200_OK;
         }
@@ -575,7 +636,7 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
         B = (L + chunk - 1) / chunk;
         B200_TRY(scratch(st, (size_t)(M * B) * sizeof(Acc), &scr, &counters));
         reduce_contig_block_kernel<Tin, Acc><<<balanced_grid(M * B, target), kRedThreads, 0, st->s>>>(
-            (const Tin*)A, L, M, (int)B, chunk, mapop, (Acc*)scr, counters, out);
+            (const Tin*)A, L, M, (int)B, chunk, mapop, (Acc*)scr, counters, out, pc);
         return B200_OK;
     }
     // strided
@@ -613,9 +674,9 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
 
 using namespace b200;
 
-extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
-                                  const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
-                                  int32_t ninstr, int32_t op, const void* init) {
+static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
+                              const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
+                              int32_t ninstr, int32_t op, const void* init, const PeerCtx* peer) {
     B200_TRY(enter(st));
     B200_TRY(check_tensor(R, "mapreduce destination"));
     if (!shape && ndim > 0) return fail(B200_INVALID_ARG, "mapreduce: null shape");
@@ -683,18 +744,21 @@ extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const 
         const void* A = P.leaves[leaf].ptr;
         const int mapop = B200_MAPOP(map, op);
         int32_t s = -1;
-        if (in_dt == B200_F32 && acc_dt == B200_F32) s = launch_fast<float, float>(st, A, K, L, M, mapop, out);
-        else if (in_dt == B200_F16 && acc_dt == B200_F32) s = launch_fast<__half, float>(st, A, K, L, M, mapop, out);
-        else if (in_dt == B200_BF16 && acc_dt == B200_F32) s = launch_fast<__nv_bfloat16, float>(st, A, K, L, M, mapop, out);
-        else if (in_dt == B200_F64 && acc_dt == B200_F64) s = launch_fast<double, double>(st, A, K, L, M, mapop, out);
-        else if (in_dt == B200_I32 && acc_dt == B200_I32) s = launch_fast<int32_t, int32_t>(st, A, K, L, M, mapop, out);
-        else if (in_dt == B200_I32 && acc_dt == B200_I64) s = launch_fast<int32_t, int64_t>(st, A, K, L, M, mapop, out);
-        else if (in_dt == B200_I64 && acc_dt == B200_I64) s = launch_fast<int64_t, int64_t>(st, A, K, L, M, mapop, out);
+        if (in_dt == B200_F32 && acc_dt == B200_F32) s = launch_fast<float, float>(st, A, K, L, M, mapop, out, peer);
+        else if (in_dt == B200_F16 && acc_dt == B200_F32) s = launch_fast<__half, float>(st, A, K, L, M, mapop, out, peer);
+        else if (in_dt == B200_BF16 && acc_dt == B200_F32) s = launch_fast<__nv_bfloat16, float>(st, A, K, L, M, mapop, out, peer);
+        else if (in_dt == B200_F64 && acc_dt == B200_F64) s = launch_fast<double, double>(st, A, K, L, M, mapop, out, peer);
+        else if (in_dt == B200_I32 && acc_dt == B200_I32) s = launch_fast<int32_t, int32_t>(st, A, K, L, M, mapop, out, peer);
+        else if (in_dt == B200_I32 && acc_dt == B200_I64) s = launch_fast<int32_t, int64_t>(st, A, K, L, M, mapop, out, peer);
+        else if (in_dt == B200_I64 && acc_dt == B200_I64) s = launch_fast<int64_t, int64_t>(st, A, K, L, M, mapop, out, peer);
         if (s >= 0) {
             B200_TRY(s);
             return finish(st, "b200_mapreduce");
         }
     }
+
+    if (peer) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce needs a full reduction of one dense array with "
+                          "f in {identity, abs, abs2}; use b200_mapreduce followed by b200_allreduce for anything else");
 
     // ---- evaluator path
     GenericPlan G{};
@@ -730,4 +794,23 @@ extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const 
     if (C.wide) reduce_program_kernel<true><<<blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint64_t*)scr, counters, out);
     else reduce_program_kernel<false><<<blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint32_t*)scr, counters, out);
     return finish(st, "b200_mapreduce");
+}
+
+extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
+                                  const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
+                                  int32_t ninstr, int32_t op, const void* init) {
+    return mapreduce_impl(st, R, shape, ndim, leaves, nleaves, program, ninstr, op, init, nullptr);
+}
+
+extern "C" int32_t b200_mapreduce_allreduce(b200_peer_t peer, b200_stream_t st, const b200_tensor* R, const int64_t* shape,
+                                            int32_t ndim, const b200_leaf* leaves, int32_t nleaves,
+                                            const uint8_t* program, int32_t ninstr, int32_t op, const void* init) {
+    if (!peer) return fail(B200_INVALID_ARG, "null peer group");
+    PeerCtx pc{};
+    B200_TRY(b200::peer_next_context(peer, st, &pc));
+    if (R && tensor_numel(R) != 1) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce produces one element");
+    int64_t n = 1;
+    for (int d = 0; d < ndim; ++d) n *= shape ? shape[d] : 0;
+    if (n == 0) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce needs a non-empty shard on every rank");
+    return mapreduce_impl(st, R, shape, ndim, leaves, nleaves, program, ninstr, op, init, &pc);
 }

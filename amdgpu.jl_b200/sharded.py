@@ -44,9 +44,12 @@ class ShardedOps:
 
     def mapreduce(self, f, op, shard, init=None):
         """All ranks receive op-fold over the whole (virtual) array of f(shard elements)."""
-        part = self.b.local_mapreduce(f, op, shard)          # one-element holder, op-neutral seeded
-        if self.world > 1:
-            self.b.allreduce(part, op)
+        fused = getattr(self.b, "fused_mapreduce", None)
+        part = fused(f, op, shard) if (fused is not None and self.world > 1) else None
+        if part is None:
+            part = self.b.local_mapreduce(f, op, shard)      # one-element holder, op-neutral seeded
+            if self.world > 1:
+                self.b.allreduce(part, op)
         if init is not None:
             part = self.b.combine_scalar(op, init, part)
         return part
@@ -64,11 +67,33 @@ class ShardedOps:
 class DeviceBackend:
     """Library kernels + NCCL through the C ABI."""
 
-    def __init__(self, comm, world_size: int, stream=None):
+    def __init__(self, comm, world_size: int, stream=None, peer=None):
         from .runtime import current_stream
         self.comm = comm
+        self.peer = peer
         self.world_size = world_size
         self.stream = stream or current_stream()
+
+    def fused_mapreduce(self, f, op, shard):
+        """Reduction and all-reduce in ONE kernel over NVLink peer memory; None when the case is
+        outside what that kernel handles (the caller then reduces locally and all-reduces)."""
+        if self.peer is None or len(shard) == 0:
+            return None
+        from . import _lib
+        from .array import ROCArray
+        from .mapreduce import _apply_f, _neutral, _op_code, _result_dtype
+        expr = _apply_f(f, shard)
+        opc = _op_code(op)
+        dt = _result_dtype(expr.dtype, opc)
+        R = ROCArray(dt, (1,) * max(1, len(expr.shape())), stream=self.stream)
+        try:
+            launch = prepared_mapreduce_allreduce(self.peer, expr, op, R, _neutral(opc, dt), self.stream)
+            launch()
+        except _lib.B200Error as e:
+            if e.code == _lib.UNSUPPORTED:
+                return None
+            raise
+        return R
 
     def local_mapreduce(self, f, op, shard):
         from .array import ROCArray
@@ -122,6 +147,42 @@ class DeviceBackend:
         check(lib.b200_accumulate_carry(self.stream.handle, C.byref(tb), C.byref(ta), _op_code(op),
                                         C.c_void_p(carry.ptr), 0, 1))
         return out_shard
+
+
+def prepared_mapreduce_allreduce(peer, expr, op, R, init, stream):
+    """Zero-argument callable issuing one fused reduce + all-reduce of `expr` into the one-element
+    array `R` (descriptors built once)."""
+    from ._lib import check, lib
+    from .broadcast import Broadcasted
+    from .mapreduce import _op_code
+    expr = Broadcasted.leaf(expr)
+    shape = expr.shape()
+    code, leaves, nleaves, keep = expr.flatten()
+    shp = (C.c_int64 * max(1, len(shape)))(*shape)
+    t = R.tensor()
+    init_buf = None if init is None else np.asarray(init, dtype=R.dtype).tobytes()
+    fn, ninstr, opc, nd = lib.b200_mapreduce_allreduce, len(code) // 2, _op_code(op), len(shape)
+
+    def launch(_keep=(keep, R, stream)):
+        check(fn(peer, stream.handle, C.byref(t), shp, nd, leaves, nleaves, code, ninstr, opc, init_buf))
+    return launch
+
+
+def init_peer(rank: int, world: int, device: int, allgather) -> C.c_void_p:
+    """Creates this rank's peer-exchange group.  `allgather(bytes) -> list[bytes]` must return
+    every rank's argument in rank order on every rank (any host channel)."""
+    from ._lib import check, lib
+    peer = C.c_void_p()
+    buf = C.create_string_buffer(64)
+    check(lib.b200_peer_create(device, rank, world, C.byref(peer), buf))
+    handles = allgather(buf.raw)
+    check(lib.b200_peer_connect(peer, b"".join(handles)))
+    return peer
+
+
+def destroy_peer(peer) -> None:
+    from ._lib import check, lib
+    check(lib.b200_peer_destroy(peer))
 
 
 def init_comm(rank: int, world: int, device: int, exchange) -> C.c_void_p:

@@ -128,6 +128,13 @@ class Dist:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t[0])
 
+    def allgather(self, payload):
+        if self.dist is None:
+            return [payload]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, payload)
+        return out
+
     def close(self):
         if self.dist is not None:
             self.dist.destroy_process_group()
@@ -271,6 +278,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-suite", action="store_true", help="skip the per-configuration kernel numbers")
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl", "none"],
+                    help="fused: reduction and all-reduce in one kernel over NVLink peer memory; nccl: reduction kernel, then "
+                         "ncclAllReduce on the same stream; none: diagnostic, ranks run their shards without any exchange")
     ap.add_argument("--case", default=None, help="run only the suite cases whose name starts with this (e.g. c3_scan) and print them")
     ap.add_argument("--shrink", type=int, default=0, help="with --case: divide the sizes by 2^SHRINK (small cases for profiler captures)")
     ap.add_argument("--reps-scale", type=float, default=1.0, help="with --case: scale the repetition counts")
@@ -312,8 +322,10 @@ def main():
     dist = Dist(rank, world)
     pkg.device_(local_rank)
     st = pkg.current_stream()
-    comm = None
-    if world > 1:
+    comm = peer = None
+    if world > 1 and args.collective == "fused":
+        peer = pkg.sharded.init_peer(rank, world, local_rank, dist.allgather)
+    elif world > 1 and args.collective == "nccl":
         comm = pkg.sharded.init_comm(rank, world, local_rank, dist.exchange)
     R, bc = pkg.random, pkg.broadcast
     first = rank * n
@@ -323,11 +335,15 @@ def main():
     zero = np.float32(0)
     expr = x.dot * y.dot + bc.exp(-bc.abs_(z))
     launches = [0]
+    fused_step = pkg.sharded.prepared_mapreduce_allreduce(peer, bc.abs2(r), "+", part, zero, st) if peer is not None else None
 
     def step():
         pkg.materialize_(r, expr)
-        pkg.mapreducedim_("abs2", "+", part, r, init=zero)
         launches[0] += 2
+        if fused_step is not None:
+            fused_step()                       # sum(abs2, r) and the all-reduce, one kernel
+            return
+        pkg.mapreducedim_("abs2", "+", part, r, init=zero)
         if comm is not None:
             pkg._lib.check(pkg._lib.lib.b200_allreduce(comm, C.c_void_p(part.ptr), 1, pkg._lib.F32, pkg._lib.RED_ADD, st.handle))
 
@@ -361,6 +377,10 @@ def main():
     ms_bc = time_loop(pkg, st, lambda: pkg.materialize_(r, expr), 10)
     ms_red = time_loop(pkg, st, lambda: pkg.mapreducedim_("abs2", "+", part, r, init=zero), 10)
     ach = 16 * n / ms_bc / 1e6
+    ms_coll = None
+    if fused_step is not None:
+        dist.barrier()
+        ms_coll = dist.max(time_loop(pkg, st, fused_step, 10))     # reduction + all-reduce in one kernel
 
     # ---- end to end through the public API with host buffers
     ne = min(n, 1 << 28)
@@ -376,15 +396,19 @@ def main():
     pkg._lib.check(pkg._lib.lib.b200_host_alloc(C.byref(hres), 4))
     xe, ye, ze, re_ = (v.view(0, ne) for v in (x, y, z, r))
     expr_e = xe.dot * ye.dot + bc.exp(-bc.abs_(ze))
+    fused_e = pkg.sharded.prepared_mapreduce_allreduce(peer, bc.abs2(re_), "+", part, zero, st) if peer is not None else None
     L = pkg._lib.lib
 
     def e2e_step():
         for (p, _), d in zip(hbuf, (xe, ye, ze)):
             pkg._lib.check(L.b200_memcpy_async(C.c_void_p(d.ptr), p, 4 * ne, st.handle))
         pkg.materialize_(re_, expr_e)
-        pkg.mapreducedim_("abs2", "+", part, re_, init=zero)
-        if comm is not None:
-            pkg._lib.check(L.b200_allreduce(comm, C.c_void_p(part.ptr), 1, pkg._lib.F32, pkg._lib.RED_ADD, st.handle))
+        if fused_e is not None:
+            fused_e()
+        else:
+            pkg.mapreducedim_("abs2", "+", part, re_, init=zero)
+            if comm is not None:
+                pkg._lib.check(L.b200_allreduce(comm, C.c_void_p(part.ptr), 1, pkg._lib.F32, pkg._lib.RED_ADD, st.handle))
         pkg._lib.check(L.b200_memcpy_async(hres, C.c_void_p(part.ptr), 4, st.handle))
         st.synchronize()          # the caller reads the scalar
     for _ in range(2):
@@ -413,6 +437,10 @@ def main():
     dist.barrier()
     if comm is not None:
         pkg.sharded.destroy_comm(comm)
+    if peer is not None:
+        pkg.device_synchronize()
+        dist.barrier()
+        pkg.sharded.destroy_peer(peer)
     dist.close()
     if rank != 0:
         return
@@ -422,14 +450,16 @@ def main():
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "elements_per_gpu": n, "l2": "inputs (12 GiB per GPU) are far larger than L2",
-                   "frac_of_8TBs_per_gpu": round(value / world / NOMINAL_HBM_GBS, 3), "check_sum_abs2": total_sq},
+                   "frac_of_8TBs_per_gpu": round(value / world / NOMINAL_HBM_GBS, 3), "check_sum_abs2": total_sq,
+                   "collective": args.collective if world > 1 else "none"},
         "roofline": {"bound": "hbm", "kernel": "ew_stream_kernel<float, MulAddExpNegAbsF> (r .= x.*y .+ exp.(-abs.(z)))",
                      "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 3),
                      "peak_source": f"{peak_kind} copy bandwidth", "traffic": round(EW_TRAFFIC_BYTES_PER_ELEM * n),
                      "traffic_source": "ncu capture at 2^26 elements scaled by the element count",
                      "ms_per_launch": round(ms_bc, 4), "algorithmic_bytes_per_launch": 16 * n,
                      "reduce_kernel": {"ms_per_launch": round(ms_red, 4), "achieved": round(4 * n / ms_red / 1e6, 1),
-                                       "frac": round(4 * n / ms_red / 1e6 / peak, 3)}},
+                                       "frac": round(4 * n / ms_red / 1e6 / peak, 3)},
+                     "fused_reduce_allreduce_ms": None if ms_coll is None else round(ms_coll, 4)},
         "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": 12 * ne, "d2h_bytes_per_step": 4,
                 "elements_per_gpu": ne, "ms_per_step": round(e2e_ms, 3)},
         "gpu_launches": timed_launches,

@@ -80,6 +80,7 @@ enum { B200_RED_ADD = 0, B200_RED_MUL = 1, B200_RED_MAX = 2, B200_RED_MIN = 3, B
 typedef struct b200_stream_s* b200_stream_t;
 typedef struct b200_event_s*  b200_event_t;
 typedef struct b200_comm_s*   b200_comm_t;
+typedef struct b200_peer_s*   b200_peer_t;
 
 /* Dense array view.  Mirrors what ROCArray hands to a kernel (src/array.jl:19-39: buffer, dims,
  * byte offset; pointer = base + offset, src/array.jl:353-354). */
@@ -253,6 +254,23 @@ int32_t b200_allreduce(b200_comm_t comm, void* buf, size_t count, int32_t dtype,
 /* gathers `count` elements from every rank into recv[rank*count ...] */
 int32_t b200_allgather(b200_comm_t comm, const void* send, void* recv, size_t count,
                        int32_t dtype, b200_stream_t st);
+
+/* Fused reduce + all-reduce over NVLink peer memory (no counterpart in the reference, which has
+ * no collective layer).  Every rank calls b200_peer_create, the 64-byte handles are gathered on
+ * the host (rank r's handle at handles[64*r]), every rank calls b200_peer_connect.  All ranks
+ * must then issue the same sequence of b200_mapreduce_allreduce calls. */
+int32_t b200_peer_create(int32_t dev, int32_t rank, int32_t nranks, b200_peer_t* out, uint8_t handle_out[64]);
+int32_t b200_peer_connect(b200_peer_t peer, const uint8_t* handles);
+int32_t b200_peer_destroy(b200_peer_t peer);
+/* mapreducedim! to ONE element followed by an all-reduce of that element over the peer group,
+ * in a single kernel: the block that completes the local reduction stores the partial into every
+ * rank's exchange slot and folds all ranks' partials in rank order (identical bits on all ranks).
+ * Restricted to a full reduction of one dense array with f in {identity, abs, abs2}; other
+ * cases return B200_UNSUPPORTED (use b200_mapreduce + b200_allreduce).  Waits are bounded. */
+int32_t b200_mapreduce_allreduce(b200_peer_t peer, b200_stream_t st, const b200_tensor* R,
+                                 const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
+                                 int32_t nleaves, const uint8_t* program, int32_t ninstr, int32_t op,
+                                 const void* init);
 
 #ifdef __cplusplus
 }

@@ -24,9 +24,15 @@ def _worker(rank, world, port, tmp):
         box = [payload]
         dist.broadcast_object_list(box, src=0)
         return box[0]
+    def allgather(payload):
+        out = [None] * world
+        dist.all_gather_object(out, payload)
+        return out
     comm = pkg.sharded.init_comm(rank, world, rank, exchange)
+    peer = pkg.sharded.init_peer(rank, world, rank, allgather)
     try:
         ops = pkg.sharded.ShardedOps(pkg.sharded.DeviceBackend(comm, world), rank, world)
+        fused = pkg.sharded.ShardedOps(pkg.sharded.DeviceBackend(comm, world, peer=peer), rank, world)
         rng = np.random.default_rng(11)                    # same stream on every rank
         n = 3_000_004
         xi = rng.integers(-100, 101, n).astype(np.int32)
@@ -40,6 +46,21 @@ def _worker(rank, world, port, tmp):
         ref = (xf.astype(np.float64) ** 2).sum()
         assert abs(sq - ref) <= 1e-5 * ref
         assert ops.mapreduce(None, "max", sf).to_host()[0] == xf.max()
+        # the same reductions through the one-kernel reduce + all-reduce over peer memory, several
+        # in a row (alternating slot banks), every rank must hold the same bits
+        for k in range(5):
+            v = (rng.random(n) * 2 - 1).astype(np.float32)
+            sv = pkg.ROCArray.from_host(v[lo:hi])
+            got = fused.mapreduce("abs2", "+", sv).to_host()[0]
+            ref = (v.astype(np.float64) ** 2).sum()
+            assert abs(got - ref) <= 1e-5 * ref, (k, got, ref)
+            assert len({g.tobytes() for g in allgather(got)}) == 1
+            assert fused.mapreduce(None, "max", sv).to_host()[0] == v.max()
+        assert fused.mapreduce(None, "+", si).to_host()[0] == xi.astype(np.int64).sum()
+        # a case the fused kernel does not cover falls back to reduce + NCCL all-reduce
+        two = fused.mapreduce(lambda t: t * t + 1, "+", sf).to_host()[0]
+        ref2 = (xf.astype(np.float64) ** 2 + 1).sum()
+        assert abs(two - ref2) <= 1e-5 * ref2
         # scans: carry stays on the device
         out = pkg.ROCArray(np.int32, hi - lo)
         ops.accumulate("+", out, si)
@@ -51,6 +72,9 @@ def _worker(rank, world, port, tmp):
         pkg.synchronize()
         (Path(tmp) / f"ok{rank}").write_text("ok")
     finally:
+        pkg.synchronize()
+        dist.barrier()
+        pkg.sharded.destroy_peer(peer)
         pkg.sharded.destroy_comm(comm)
         dist.destroy_process_group()
 
