@@ -673,14 +673,13 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         SegPlan sp{};
         sp.nvec = pl.L * (int64_t)sizeof(T) / 16;
         int64_t grid = resident_blocks(scan_segment_kernel<T, OP>, kSegThreads, 0, st->dev);
-        // segments: 1..3 sub-tiles of 16 KiB; short vectors get smaller segments so that every
-        // block has work; 48 KiB measured best for long ones (look-backs are rare enough, and
-        // the live segments of all blocks stay far below the L2 capacity)
+        // segments are whole sub-tiles of 16 KiB: 48 KiB measured best for long vectors (look-backs
+        // are rare enough and the live segments of all blocks stay far below the L2 capacity)
         const int64_t subv = kSubTileVecs;
         const int64_t nsub = (sp.nvec + subv - 1) / subv;
-        int64_t per = nsub / (grid * 3);
+        int64_t per = nsub / (grid * 3);     // short vectors: smaller segments, so that every block has work
         if (per < 1) per = 1;
-        if (per > 3) per = 3;        // two segments per block are live in L2: 2 x 48 KiB x 444 blocks = 43 MB
+        if (per > 3) per = 3;     // two segments per block are live in L2: 2 x 48 KiB x 444 blocks = 43 MB
         sp.seg_vecs = per * subv;
         sp.nsegs = (sp.nvec + sp.seg_vecs - 1) / sp.seg_vecs;
         sp.inclusive = pl.inclusive;

@@ -407,22 +407,30 @@ __device__ __forceinline__ void strided_body(const Tin* A, const StridedPlan& pl
         __syncthreads();
         if (s_last) {
             __threadfence();
-            if (ty == 0 && k0 < pl.K) {
+            // every row group folds its share of the strips (strip s goes to group s % ly), then
+            // the groups are combined through shared memory in group order: a fixed order, and
+            // the whole block takes part instead of one warp
+            Acc part[V];
 #pragma unroll
-                for (int k = 0; k < V; ++k) {
-                    // the loads are independent: issue eight at a time, fold them in strip order
-                    Acc p = red_identity<Acc, OP>();
-                    const Acc* src = partials + tile * pl.nstrips * width + tx * V + k;
-                    for (int s0 = 0; s0 < pl.nstrips; s0 += 8) {
-                        Acc t[8];
+            for (int k = 0; k < V; ++k) part[k] = red_identity<Acc, OP>();
+            if (lane_on && k0 < pl.K) {
+                const Acc* src = partials + tile * pl.nstrips * width + tx * V;
+                for (int s = ty; s < pl.nstrips; s += pl.ly) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            t[j] = (s0 + j < pl.nstrips) ? __ldcg(src + (int64_t)(s0 + j) * width) : red_identity<Acc, OP>();
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) p = red_apply<Acc, OP>(p, t[j]);
-                    }
-                    finalize<Acc, OP>(out, k0 + k + pl.K * m, p);
+                    for (int k = 0; k < V; ++k) part[k] = red_apply<Acc, OP>(part[k], __ldcg(src + (int64_t)s * width + k));
                 }
+            }
+            if (lane_on) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) smem[(ty * pl.kx + tx) * V + k] = part[k];
+            }
+            __syncthreads();
+            if (ty == 0 && k0 < pl.K) {
+                for (int y = 1; y < pl.ly; ++y)
+#pragma unroll
+                    for (int k = 0; k < V; ++k) part[k] = red_apply<Acc, OP>(part[k], smem[(y * pl.kx + tx) * V + k]);
+#pragma unroll
+                for (int k = 0; k < V; ++k) finalize<Acc, OP>(out, k0 + k + pl.K * m, part[k]);
             }
         }
         __syncthreads();
