@@ -26,9 +26,10 @@ class _Managed:
     __slots__ = ("ptr", "nbytes", "stream", "freed", "__weakref__")
 
     def __init__(self, nbytes: int, stream: Stream):
-        self.ptr = pool_alloc(nbytes, stream)
+        self.ptr, self.freed = 0, True          # a failed allocation must leave a harmless object
         self.nbytes = nbytes
         self.stream = stream
+        self.ptr = pool_alloc(nbytes, stream)
         self.freed = False
 
     def free(self) -> None:

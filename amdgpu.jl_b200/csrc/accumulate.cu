@@ -921,3 +921,33 @@ extern "C" int32_t b200_accumulate_noalloc(b200_stream_t st, const b200_tensor* 
 }
 
 B200_DEFINE_PHASE_READER(b200_debug_phases_scan)
+
+// Self-test of the bounded wait: runs ONE tile of the chained scan whose ticket says it is tile 1
+// while tile 0 never exists, with a poll budget of `polls`.  The block gives up after that many
+// polls, latches B200_LOOKBACK_TIMEOUT and returns; the next b200_stream_sync reports it and the
+// context stays usable.  Nothing faults and nothing spins without a limit.
+extern "C" int32_t b200_selftest_wait_timeout(b200_stream_t st, uint32_t polls) {
+    B200_TRY(enter(st));
+    if (polls == 0 || polls > (1u << 20)) return fail(B200_INVALID_ARG, "poll budget must be in 1..2^20");
+    constexpr int TILE = kScanThreads * kScanVecs * 4;
+    void* scr = nullptr;
+    unsigned int* counters = nullptr;
+    const size_t data_bytes = 2 * (size_t)TILE * sizeof(int32_t);
+    const size_t sbytes = 256 + TileState<int32_t>::bytes(2) + 2 * data_bytes;
+    B200_TRY(scratch(st, sbytes, &scr, &counters));
+    B200_CUDA(cudaMemsetAsync(scr, 0, sbytes, st->s));
+    unsigned char* base = reinterpret_cast<unsigned char*>(scr);
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(base);
+    const unsigned int one = 1;
+    B200_CUDA(cudaMemcpyAsync(ticket, &one, sizeof one, cudaMemcpyHostToDevice, st->s));   // first ticket handed out is 1
+    int32_t* in = reinterpret_cast<int32_t*>(base + 256 + 256);
+    int32_t* out = in + 2 * TILE;
+    ScanPlan pl{};
+    pl.K = 1; pl.L = 2 * TILE; pl.M = 1;
+    pl.tiles_per_col = 2; pl.ntiles = 2;
+    pl.vec_ok = 1; pl.inclusive = 1; pl.has_init = 0;
+    pl.max_polls = polls;
+    scan_lookback_kernel<int32_t, B200_RED_ADD><<<1, kScanThreads, 0, st->s>>>(in, out, pl, base + 256, ticket, device_error_word(st->dev));
+    B200_CUDA(cudaMemsetAsync(ticket, 0, sizeof(unsigned int), st->s));
+    return finish(st, "b200_selftest_wait_timeout");
+}

@@ -10,6 +10,7 @@
 #include "program.cuh"
 
 #include <cstring>
+#include <type_traits>
 #include <vector>
 
 namespace b200 {
@@ -44,6 +45,77 @@ uint64_t scalar_to_class(int32_t dt, uint64_t bits) {
         case B200_U16: return bits & 0xffff;
         case B200_F32: case B200_I32: case B200_U32: return bits & 0xffffffffu;
         default: return bits;
+    }
+}
+
+// Host-side conversion of a scalar between element types (class representation in and out), with
+// the same rounding as the device CONVERT: used to fold `convert(T, scalar)` at compile time so
+// that e.g. `2 .* x` with an Int64 literal and a Float32 array still takes a streaming kernel.
+static uint16_t float_to_half_bits(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    const uint32_t sign = (x >> 16) & 0x8000u;
+    const int32_t exp = (int32_t)((x >> 23) & 0xff) - 127 + 15;
+    uint32_t man = x & 0x7fffffu;
+    if (((x >> 23) & 0xff) == 0xff) return (uint16_t)(sign | 0x7c00u | (man ? 0x200u : 0));
+    if (exp >= 31) return (uint16_t)(sign | 0x7c00u);
+    if (exp <= 0) {
+        if (exp < -10) return (uint16_t)sign;
+        man |= 0x800000u;
+        const int shift = 14 - exp;
+        uint32_t h = man >> shift;
+        const uint32_t rem = man & ((1u << shift) - 1), half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (h & 1))) ++h;
+        return (uint16_t)(sign | h);
+    }
+    uint32_t h = ((uint32_t)exp << 10) | (man >> 13);
+    const uint32_t rem = man & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (h & 1))) ++h;
+    return (uint16_t)(sign | h);
+}
+
+static uint64_t convert_scalar_class(int src, int dst, uint64_t cls) {
+    double d = 0;
+    int64_t i = 0;
+    uint64_t u = 0;
+    const int sc = dtype_class(src), dc = dtype_class(dst);
+    const bool src_float = sc == CF32 || sc == CF64;
+    if (sc == CF32) { uint32_t b = (uint32_t)cls; float f; memcpy(&f, &b, 4); d = f; }
+    else if (sc == CF64) memcpy(&d, &cls, 8);
+    else if (sc == CI32) { i = (int32_t)(uint32_t)cls; u = (uint64_t)i; d = (double)i; }
+    else if (sc == CI64) { i = (int64_t)cls; u = (uint64_t)i; d = (double)i; }
+    else if (sc == CU32) { u = (uint32_t)cls; i = (int64_t)u; d = (double)u; }
+    else { u = cls; i = (int64_t)u; d = (double)u; }
+    if (src_float) { i = (int64_t)d; u = (uint64_t)i; }
+    uint64_t out = 0;
+    switch (dc) {
+        case CF32: {
+            float f = (sc == CF32 || sc == CF64) ? (float)d : (sc == CU64 ? (float)u : (float)i);
+            if (dst == B200_F16) f = half_bits_to_float(float_to_half_bits(f));
+            uint32_t b;
+            memcpy(&b, &f, 4);
+            if (dst == B200_BF16) {
+                const uint32_t lsb = (b >> 16) & 1u;
+                if ((b & 0x7f800000u) != 0x7f800000u) b += 0x7fffu + lsb;
+                b &= 0xffff0000u;
+            }
+            out = b;
+            break;
+        }
+        case CF64: { double v = src_float ? d : (sc == CU64 ? (double)u : (double)i); memcpy(&out, &v, 8); break; }
+        case CI32: out = (uint32_t)(int32_t)i; break;
+        case CI64: out = (uint64_t)i; break;
+        case CU32: out = (uint32_t)u; break;
+        default: out = u; break;
+    }
+    return scalar_to_class(dst, dst == B200_F16 || dst == B200_BF16 ? class_to_storage(dst, out) : out);
+}
+
+uint64_t class_to_storage(int32_t dt, uint64_t cls) {
+    switch (dt) {
+        case B200_F16: { uint32_t b = (uint32_t)cls; float f; memcpy(&f, &b, 4); return float_to_half_bits(f); }
+        case B200_BF16: return (cls >> 16) & 0xffff;
+        default: return cls;
     }
 }
 
@@ -109,7 +181,25 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
                 if (sp < 1) return fail(B200_INVALID_ARG, "instruction %d: empty stack", pc);
                 if (arg >= B200_DTYPE_COUNT) return fail(B200_UNSUPPORTED, "instruction %d: unknown dtype %d", pc, arg);
                 const int src = stack[sp - 1];
-                if (src != arg) emit(op, (src << 4) | arg);
+                if (src != arg) {
+                    // convert(T, scalar) is folded here: the scalar leaf is replaced by a converted copy
+                    const bool prev_is_scalar_leaf = nout > 0 && P.code[2 * (nout - 1)] == B200_OP_LEAF &&
+                                                     P.leaves[P.code[2 * (nout - 1) + 1]].is_scalar;
+                    if (prev_is_scalar_leaf && P.nleaves < B200_MAX_LEAVES && arg != B200_BOOL) {
+                        const LeafDesc& old = P.leaves[P.code[2 * (nout - 1) + 1]];
+                        LeafDesc& nw = P.leaves[P.nleaves];
+                        nw = LeafDesc{};
+                        nw.dtype = arg;
+                        nw.is_scalar = 1;
+                        nw.scalar = convert_scalar_class(old.dtype, arg, old.scalar);
+                        P.code[2 * (nout - 1) + 1] = (uint8_t)P.nleaves;
+                        ++P.nleaves;
+                        const int c = dtype_class(arg);
+                        if (c == CF64 || c == CI64 || c == CU64) wide = true;
+                    } else {
+                        emit(op, (src << 4) | arg);
+                    }
+                }
                 stack[sp - 1] = arg;
                 break;
             }
@@ -151,6 +241,15 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
         int c = dtype_class(final_dtype);
         if (c == CF64 || c == CI64 || c == CU64) wide = true;
         stack[0] = final_dtype;
+    }
+    // width of the evaluator: only what the final program really touches counts
+    auto is_wide = [](int dt) { const int c = dtype_class(dt); return c == CF64 || c == CI64 || c == CU64; };
+    wide = false;
+    for (int pc = 0; pc < nout; ++pc) {
+        const int o = P.code[2 * pc], a = P.code[2 * pc + 1];
+        if (o == B200_OP_LEAF) wide = wide || is_wide(P.leaves[a].dtype);
+        else if (o == B200_OP_CONVERT) wide = wide || is_wide(a >> 4) || is_wide(a & 15);
+        else wide = wide || is_wide(a);
     }
     P.ninstr = nout;
     P.linear = linear ? 1 : 0;
@@ -214,6 +313,62 @@ template <> struct Elem<__nv_bfloat16> {
     static __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 };
 
+template <> struct Elem<int32_t> {
+    using C = int32_t;
+    static __device__ __forceinline__ int32_t up(int32_t v) { return v; }
+    static __device__ __forceinline__ int32_t down(int32_t v) { return v; }
+    static __device__ __forceinline__ int32_t rnd(int32_t v) { return v; }
+};
+template <> struct Elem<int64_t> {
+    using C = int64_t;
+    static __device__ __forceinline__ int64_t up(int64_t v) { return v; }
+    static __device__ __forceinline__ int64_t down(int64_t v) { return v; }
+    static __device__ __forceinline__ int64_t rnd(int64_t v) { return v; }
+};
+
+// One operator of the fixed set applied to arrays and at most one scalar: f(x), x o y, x o s,
+// s o x.  The operator is a run-time value; it is switched on once per 16-byte vector.
+enum { MODE_UNARY = 0, MODE_AA = 1, MODE_AS = 2, MODE_SA = 3 };
+template <typename T>
+struct OneOpF {
+    int op, mode;
+    typename Elem<T>::C s;
+    template <int V>
+    __device__ __forceinline__ Vec<T, V> vec(const Vec<T, V>& a, const Vec<T, V>& b) const {
+        using E = Elem<T>;
+        using C = typename E::C;
+        using A = Arith<C>;
+        Vec<T, V> r;
+#define B200_EW(EXPR)                                                         \
+    _Pragma("unroll") for (int k = 0; k < V; ++k) {                           \
+        const C x = (mode == MODE_SA) ? s : E::up(a.v[k]);                    \
+        const C y = (mode == MODE_AS) ? s : (mode == MODE_SA ? E::up(a.v[k]) : E::up(b.v[k])); \
+        (void)y;                                                              \
+        r.v[k] = E::down(EXPR);                                               \
+    }                                                                         \
+    break;
+        switch (op) {
+            case B200_OP_ADD: B200_EW(A::add(x, y))
+            case B200_OP_SUB: B200_EW(A::sub(x, y))
+            case B200_OP_MUL: B200_EW(A::mul(x, y))
+            case B200_OP_DIV: B200_EW(A::div(x, y))
+            case B200_OP_MAX: B200_EW(A::max(x, y))
+            case B200_OP_MIN: B200_EW(A::min(x, y))
+            case B200_OP_ABS: B200_EW(A::abs(x))
+            case B200_OP_ABS2: B200_EW(E::rnd(A::mul(x, x)))
+            case B200_OP_EXP: B200_EW(A::exp(x))
+            case B200_OP_NEG: B200_EW(A::neg(x))
+            default: r = a; break;
+        }
+#undef B200_EW
+        return r;
+    }
+    __device__ __forceinline__ T operator()(T x, T y, T) const {
+        Vec<T, 1> a{{x}}, b{{y}};
+        return vec<1>(a, b).v[0];
+    }
+};
+
 // z = a*x + y, multiply and add rounded separately (Base does not contract `a .* x .+ y`).
 template <typename T>
 struct AxpyF {
@@ -236,6 +391,9 @@ struct MulAddExpNegAbsF {
         return E::down(A::add(p, e));
     }
 };
+
+template <typename F, typename = void> struct HasVec : std::false_type {};
+template <typename T> struct HasVec<OneOpF<T>, void> : std::true_type {};
 
 constexpr int kEwThreads = 256;
 constexpr int kEwUnroll = 4;
@@ -262,9 +420,13 @@ ew_stream_kernel(T* out, const T* in0, const T* in1, const T* in2, F f, int64_t 
             for (int u = 0; u < kEwUnroll; ++u) {
                 const int64_t vi = base / V + (int64_t)u * kEwThreads + threadIdx.x;
                 VT r;
+                if constexpr (HasVec<F>::value) {
+                    r = f.template vec<V>(a[u], NIN > 1 ? b[u] : a[u]);
+                } else {
 #pragma unroll
-                for (int k = 0; k < V; ++k)
-                    r.v[k] = f(a[u].v[k], NIN > 1 ? b[u].v[k] : a[u].v[k], NIN > 2 ? c[u].v[k] : a[u].v[k]);
+                    for (int k = 0; k < V; ++k)
+                        r.v[k] = f(a[u].v[k], NIN > 1 ? b[u].v[k] : a[u].v[k], NIN > 2 ? c[u].v[k] : a[u].v[k]);
+                }
                 __stcs(reinterpret_cast<uint4*>(out) + vi, __builtin_bit_cast(uint4, r));
             }
         } else {
@@ -316,8 +478,10 @@ static int build_tree(const ProgramDesc& P, std::vector<Node>& nodes) {
 template <typename T>
 static typename Elem<T>::C scalar_as(uint64_t cls) {
     using C = typename Elem<T>::C;
-    if (sizeof(C) == 4) { uint32_t u = (uint32_t)cls; float f; memcpy(&f, &u, 4); return (C)f; }
-    double d; memcpy(&d, &cls, 8); return (C)d;
+    if constexpr (std::is_same<C, float>::value) { uint32_t u = (uint32_t)cls; float f; memcpy(&f, &u, 4); return f; }
+    else if constexpr (std::is_same<C, double>::value) { double d; memcpy(&d, &cls, 8); return d; }
+    else if constexpr (std::is_same<C, int32_t>::value) return (int32_t)(uint32_t)cls;
+    else return (int64_t)cls;
 }
 
 template <typename T>
@@ -327,6 +491,33 @@ static bool try_fixed(b200_stream_t st, const Compiled& C, const std::vector<Nod
     auto is_sc = [&](int i) { return i >= 0 && N[i].op == B200_OP_LEAF && P.leaves[N[i].arg].is_scalar; };
     auto ptr = [&](int i) { return P.leaves[N[i].arg].ptr; };
     const Node& r = N[root];
+    // one operator over arrays and at most one scalar
+    if (r.nk == 1 && r.op != B200_OP_CONVERT && is_arr(r.kid[0])) {
+        if (r.op == B200_OP_EXP && !std::is_floating_point<typename Elem<T>::C>::value) return false;
+        OneOpF<T> f{r.op, MODE_UNARY, typename Elem<T>::C(0)};
+        launch_stream<T, OneOpF<T>, 1>(st, out, ptr(r.kid[0]), nullptr, nullptr, f, n);
+        return true;
+    }
+    if (r.nk == 2) {
+        const int p = r.kid[0], q = r.kid[1];
+        if (r.op == B200_OP_DIV && !std::is_floating_point<typename Elem<T>::C>::value) return false;
+        if (is_arr(p) && is_arr(q)) {
+            OneOpF<T> f{r.op, MODE_AA, typename Elem<T>::C(0)};
+            launch_stream<T, OneOpF<T>, 2>(st, out, ptr(p), ptr(q), nullptr, f, n);
+            return true;
+        }
+        if (is_arr(p) && is_sc(q)) {
+            OneOpF<T> f{r.op, MODE_AS, scalar_as<T>(P.leaves[N[q].arg].scalar)};
+            launch_stream<T, OneOpF<T>, 1>(st, out, ptr(p), nullptr, nullptr, f, n);
+            return true;
+        }
+        if (is_sc(p) && is_arr(q)) {
+            OneOpF<T> f{r.op, MODE_SA, scalar_as<T>(P.leaves[N[p].arg].scalar)};
+            launch_stream<T, OneOpF<T>, 1>(st, out, ptr(q), nullptr, nullptr, f, n);
+            return true;
+        }
+    }
+    if (!std::is_floating_point<typename Elem<T>::C>::value) return false;
     if (r.op != B200_OP_ADD) return false;
     for (int side = 0; side < 2; ++side) {
         const int m = r.kid[side], o = r.kid[1 - side];
@@ -378,8 +569,10 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
     // Hard-wired kernels: every array leaf dense, same dtype as the destination, no conversions.
     if (C.P.linear) {
         bool uniform = true;
-        for (int k = 0; k < nleaves; ++k) if (C.P.leaves[k].dtype != out->dtype) uniform = false;
-        for (int pc = 0; pc < C.P.ninstr; ++pc) if (C.P.code[2 * pc] == B200_OP_CONVERT) uniform = false;
+        for (int pc = 0; pc < C.P.ninstr; ++pc) {
+            if (C.P.code[2 * pc] == B200_OP_CONVERT) uniform = false;
+            if (C.P.code[2 * pc] == B200_OP_LEAF && C.P.leaves[C.P.code[2 * pc + 1]].dtype != out->dtype) uniform = false;
+        }
         if (uniform) {
             std::vector<Node> nodes;
             int root = build_tree(C.P, nodes);
@@ -389,6 +582,8 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
                 case B200_F64: done = try_fixed<double>(st, C, nodes, root, out->ptr, n); break;
                 case B200_F16: done = try_fixed<__half>(st, C, nodes, root, out->ptr, n); break;
                 case B200_BF16: done = try_fixed<__nv_bfloat16>(st, C, nodes, root, out->ptr, n); break;
+                case B200_I32: done = try_fixed<int32_t>(st, C, nodes, root, out->ptr, n); break;
+                case B200_I64: done = try_fixed<int64_t>(st, C, nodes, root, out->ptr, n); break;
                 default: break;
             }
             if (done) return finish(st, "b200_broadcast");

@@ -1,0 +1,90 @@
+"""``findall`` / logical indexing and ``reverse``.
+
+Mirrors src/kernels/indexing.jl:8-36 (``findall(bools)`` = cumsum of the mask, read its last
+element on the host, scatter the indices; ``xs[bools]``) and src/kernels/reverse.jl:59-122
+(``reverse`` / ``reverse!`` along ``dims``).  ``findall`` of an N-d mask returns 1-based LINEAR
+indices in column-major order (the reference returns the equivalent ``CartesianIndex`` values).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import check, lib
+from .accumulate import accumulate_
+from .array import ROCArray, copyto_
+from .broadcast import Broadcasted, materialize_
+from .runtime import Stream, current_stream
+
+
+def _positions(bools: ROCArray, stream: Stream):
+    if bools.dtype != np.bool_:
+        raise TypeError("the mask must be a Bool array")
+    flat = bools.reshape(bools.size)
+    as_int = ROCArray(np.int64, flat.dims, stream=stream)
+    code = bytes((0, 0, 1, 7))                      # LEAF 0, CONVERT -> Int64
+    leaves = Broadcasted.leaf(flat).flatten()[1]
+    t = as_int.tensor()
+    check(lib.b200_broadcast(stream.handle, C.byref(t), leaves, 1, code, 2))
+    idx = accumulate_("+", as_int, as_int, init=None, stream=stream)
+    n = int(idx.view(idx.size - 1, idx.size).to_host(stream)[0]) if idx.size else 0     # blocking read, like indices[end]
+    return flat, idx, n
+
+
+def findall(bools: ROCArray, stream: Stream | None = None) -> ROCArray:
+    """``findall(bools)`` (src/kernels/indexing.jl:8-36)."""
+    st = stream or current_stream()
+    flat, idx, n = _positions(bools, st)
+    ys = ROCArray(np.int64, (n,), stream=st)
+    if n:
+        ty, tb, ti = ys.tensor(), flat.tensor(), idx.tensor()
+        check(lib.b200_compact(st.handle, C.byref(ty), C.byref(tb), C.byref(ti), None))
+    idx.unsafe_free_()
+    return ys
+
+
+def getindex_mask(xs: ROCArray, bools: ROCArray, stream: Stream | None = None) -> ROCArray:
+    """``xs[bools]`` (logical indexing, src/kernels/indexing.jl:1-6)."""
+    if xs.size != bools.size:
+        raise IndexError("mask and array differ in length")
+    st = stream or current_stream()
+    flat, idx, n = _positions(bools, st)
+    ys = ROCArray(xs.dtype, (n,), stream=st)
+    if n:
+        ty, tb, ti, tv = ys.tensor(), flat.tensor(), idx.tensor(), xs.reshape(xs.size).tensor()
+        check(lib.b200_compact(st.handle, C.byref(ty), C.byref(tb), C.byref(ti), C.byref(tv)))
+    idx.unsafe_free_()
+    return ys
+
+
+def _mask(x: ROCArray, dims) -> int:
+    if dims is None:
+        dims = range(1, x.ndim + 1)
+    elif isinstance(dims, (int, np.integer)):
+        dims = (int(dims),)
+    m = 0
+    for d in dims:
+        if not 1 <= d <= max(1, x.ndim):
+            raise ValueError(f"dimension out of range: {d}")
+        m |= 1 << (d - 1)
+    return m
+
+
+def reverse(x: ROCArray, dims=None, stream: Stream | None = None) -> ROCArray:
+    """``reverse(x; dims)`` (src/kernels/reverse.jl:91-100): out of place."""
+    st = stream or current_stream()
+    y = x.similar()
+    ty, tx = y.tensor(), x.tensor()
+    check(lib.b200_reverse(st.handle, C.byref(ty), C.byref(tx), _mask(x, dims)))
+    return y
+
+
+def reverse_(x: ROCArray, dims=None, stream: Stream | None = None) -> ROCArray:
+    """``reverse!(x; dims)`` (src/kernels/reverse.jl:102-122); goes through a device copy."""
+    st = stream or current_stream()
+    tmp = x.copy()
+    tx, tt = x.tensor(), tmp.tensor()
+    check(lib.b200_reverse(st.handle, C.byref(tx), C.byref(tt), _mask(x, dims)))
+    tmp.unsafe_free_()
+    return x

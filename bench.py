@@ -196,6 +196,21 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
         if want("c1_cumsum"):
             rec("c1_cumsum_2p24_f32", 8 * n, time_loop(pkg, st, rotate([pkg.accumulate_prepared("+", z, x) for x, _, z in sets]), reps(200)))
         del sets
+    # the same kind of expression through the generic evaluator (a tree the hard-wired kernels do
+    # not match): how fast an arbitrary fused broadcast runs
+    if want("gen"):
+        n = (1 << 26) >> shrink
+        xs = [R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM11, seed=4, stream_id=k) for k in range(3)]
+        out_ = pkg.ROCArray(np.float32, n)
+        bcm = pkg.broadcast
+        tree = xs[0].dot * xs[1].dot + bcm.exp(-bcm.abs_(xs[2])) + np.float32(0.25)
+        rec("gen_evaluator_x*y+exp(-abs(z))+c_2p26_f32", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(out_, tree), reps(20)))
+        tree2 = bcm.maximum(xs[0].dot - xs[1].dot, xs[2].dot * np.float32(2))
+        rec("gen_evaluator_max(x-y,2z)_2p26_f32", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(out_, tree2), reps(20)))
+        xi = R.fill_random_(pkg.ROCArray(np.int32, n), R.INTEGERS, seed=2, lo=-100, hi=100)
+        outd = pkg.ROCArray(np.float64, n)
+        rec("gen_evaluator_i32*f32->f64_2p26", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(outd, xi.dot * xs[0].dot * 1.5), reps(20)))
+        del xs, out_, xi, outd
     # config 2: 8192 x 8192 matrices
     if want("c2"):
         m = 8192 >> (shrink // 2)

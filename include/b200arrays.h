@@ -234,6 +234,15 @@ int32_t b200_sort(b200_stream_t st, const b200_tensor* x, int32_t rev);
  * receives the 1-based stable permutation; x is left untouched */
 int32_t b200_sortperm(b200_stream_t st, const b200_tensor* ix, const b200_tensor* x, int32_t rev);
 
+/* replaces the scatter kernel of findall / logical indexing (src/kernels/indexing.jl:8-36).
+ * `indices` = cumsum of the Bool mask as Int64 (b200_accumulate).  values == NULL: ys (Int64)
+ * receives the 1-based linear indices of the true entries; otherwise ys receives values[mask]. */
+int32_t b200_compact(b200_stream_t st, const b200_tensor* ys, const b200_tensor* bools,
+                     const b200_tensor* indices, const b200_tensor* values);
+/* replaces _reverse! (src/kernels/reverse.jl:59-87): y = x flipped along the dimensions whose bit
+ * is set in dims_mask (bit 0 = first dimension); y and x must not alias. */
+int32_t b200_reverse(b200_stream_t st, const b200_tensor* y, const b200_tensor* x, uint32_t dims_mask);
+
 /* replaces rand!/randn! for the synthetic workloads (src/random.jl:30-70): element i of `out`
  * becomes gen(seed, stream_id, first_index + i); dist 0: U[0,1), 1: U[-1,1), 2: N(0,1),
  * 3: integers in [lo,hi], 4: raw low bits.  Counter based, so any slice can be regenerated. */
@@ -254,6 +263,12 @@ int32_t b200_allreduce(b200_comm_t comm, void* buf, size_t count, int32_t dtype,
 /* gathers `count` elements from every rank into recv[rank*count ...] */
 int32_t b200_allgather(b200_comm_t comm, const void* send, void* recv, size_t count,
                        int32_t dtype, b200_stream_t st);
+
+/* Self-test of the bounded device-side waits (no counterpart in the reference, whose device-side
+ * errors are reported through its exception word, src/device/exceptions.jl:27-66): one scan tile
+ * waits for a predecessor that never publishes, gives up after `polls` polls and latches
+ * B200_LOOKBACK_TIMEOUT, which the next b200_stream_sync returns.  No fault, no unbounded spin. */
+int32_t b200_selftest_wait_timeout(b200_stream_t st, uint32_t polls);
 
 /* Fused reduce + all-reduce over NVLink peer memory (no counterpart in the reference, which has
  * no collective layer).  Every rank calls b200_peer_create, the 64-byte handles are gathered on

@@ -1,0 +1,39 @@
+"""findall / logical indexing / reverse against NumPy (the reference's tests:
+test/hip_rocarray/indexing.jl:5-18, test/hip_rocarray/reverse.jl:5-51)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_findall_and_logical_indexing(gpu):
+    rng = np.random.default_rng(0)
+    for shape in ((0,), (1,), (10,), (4097,), (33, 77), (5, 6, 7), (1_000_003,)):
+        b = rng.random(shape) < 0.3
+        x = rng.random(shape).astype(np.float32)
+        bd, xd = gpu.ROCArray.from_host(b), gpu.ROCArray.from_host(x)
+        want = np.flatnonzero(b.reshape(-1, order="F")) + 1
+        got = gpu.findall(bd)
+        assert got.dtype == np.int64 and np.array_equal(got.to_host(), want), shape
+        assert np.array_equal(gpu.getindex_mask(xd, bd).to_host(), x.reshape(-1, order="F")[want - 1]), shape
+    assert gpu.findall(gpu.ROCArray.from_host(np.zeros(100, bool))).dims == (0,)
+    assert np.array_equal(gpu.findall(gpu.ROCArray.from_host(np.ones(100, bool))).to_host(), np.arange(1, 101))
+
+
+def test_reverse(gpu):
+    rng = np.random.default_rng(1)
+    for dt in (np.float32, np.int64, np.float16, np.uint8):
+        v = (rng.random(10_001) * 100).astype(dt)
+        vd = gpu.ROCArray.from_host(v)
+        assert np.array_equal(gpu.reverse(vd).to_host(), v[::-1])
+        assert np.array_equal(vd.to_host(), v)
+        assert gpu.reverse_(vd) is vd and np.array_equal(vd.to_host(), v[::-1])
+    a = rng.random((7, 5, 3)).astype(np.float32)
+    ad = gpu.ROCArray.from_host(a)
+    assert np.array_equal(gpu.reverse(ad).to_host(), a[::-1, ::-1, ::-1])
+    assert np.array_equal(gpu.reverse(ad, dims=1).to_host(), a[::-1])
+    assert np.array_equal(gpu.reverse(ad, dims=2).to_host(), a[:, ::-1])
+    assert np.array_equal(gpu.reverse(ad, dims=(1, 3)).to_host(), a[::-1, :, ::-1])
+    assert np.array_equal(gpu.reverse_(ad, dims=3).to_host(), a[:, :, ::-1])
+    with pytest.raises(ValueError):
+        gpu.reverse(ad, dims=4)

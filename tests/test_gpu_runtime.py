@@ -98,3 +98,20 @@ def test_errors_are_reported_not_fatal(gpu):
     assert st == gpu._lib.UNSUPPORTED
     # the context is still usable afterwards
     assert float(gpu.sum(x)) == 8.0
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(gpu):
+    """A device-side wait that can never be satisfied (its flag is never set) runs out of its
+    small poll budget, the kernel returns, and the error surfaces from the next synchronisation
+    as a status - the way the reference surfaces device exceptions at synchronize
+    (src/highlevel.jl:40).  Nothing traps or hangs; later work on the same context is fine."""
+    L = gpu._lib
+    st = gpu.current_stream()
+    assert L.lib.b200_selftest_wait_timeout(st.handle, 2000) == L.OK
+    with pytest.raises(gpu.B200Error) as ei:
+        st.synchronize()
+    assert ei.value.code == L.LOOKBACK_TIMEOUT
+    st.synchronize()                                    # the latched word was cleared by the report
+    x = gpu.ROCArray.from_host(np.arange(100_000, dtype=np.int32))
+    assert np.array_equal(gpu.cumsum(x).to_host(), np.cumsum(np.arange(100_000, dtype=np.int32), dtype=np.int32))
+    assert gpu.sum(x) == 100_000 * 99_999 // 2
