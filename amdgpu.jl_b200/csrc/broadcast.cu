@@ -251,6 +251,19 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
         else if (o == B200_OP_CONVERT) wide = wide || is_wide(a >> 4) || is_wide(a & 15);
         else wide = wide || is_wide(a);
     }
+    // device code: one handler number per instruction
+    for (int pc = 0; pc < nout; ++pc) {
+        const int o = P.code[2 * pc], a = P.code[2 * pc + 1];
+        int h, arg = a;
+        if (o == B200_OP_LEAF) h = (a < kPrefetch) ? kHPre0 + a : kHLeafMem;
+        else if (o == B200_OP_CONVERT) h = kHConvert;
+        else {
+            h = kHOps + dtype_class(a) * kNumOps + (o - B200_OP_ADD);
+            arg = dtype_is_narrow(a) ? a : 0xff;
+        }
+        P.hcode[2 * pc] = (uint8_t)h;
+        P.hcode[2 * pc + 1] = (uint8_t)arg;
+    }
     P.ninstr = nout;
     P.linear = linear ? 1 : 0;
     P.vec_ok = (linear && vec_ok) ? 1 : 0;

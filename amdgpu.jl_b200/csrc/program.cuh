@@ -1,10 +1,11 @@
 // Elementwise programs: host-side validation ("compile") of the postfix byte code that the
 // C ABI accepts, and the device-side evaluator shared by the broadcast and mapreduce kernels.
 //
-// The evaluator is a stack machine whose stack lives in REGISTERS: the stack pointer selects
-// one of a handful of statically indexed code paths, so no slot is ever addressed dynamically
-// and nothing spills to local memory.  Each instruction is decoded once per thread for a
-// vector of kVec consecutive elements.
+// The evaluator is a stack machine whose stack lives in REGISTERS: the top of the stack is
+// always the same named register vector, pushes and pops shift the (at most five) live slots
+// with plain moves, so no slot is ever addressed dynamically, nothing goes to local memory and
+// every instruction is ONE indirect branch on a handler number that the host computed.  Each
+// instruction is decoded once per thread for a vector of kVec consecutive elements.
 #pragma once
 #include "common.cuh"
 
@@ -54,9 +55,13 @@ struct ProgramDesc {
     int32_t  vec_ok;      // ... and 4-element accesses are aligned for every array leaf
     int32_t  _pad;
     int64_t  shape[B200_MAX_DIMS];
-    uint8_t  code[2 * (B200_MAX_PROGRAM + 2)];
+    uint8_t  code[2 * (B200_MAX_PROGRAM + 2)];    // validated (opcode, dtype) pairs, for the host
+    uint8_t  hcode[2 * (B200_MAX_PROGRAM + 2)];   // (handler, operand) pairs, what the device runs
     LeafDesc leaves[B200_MAX_LEAVES];
 };
+
+// Handler numbers of the device evaluator.  Operators: kHOps + class * kNumOps + (opcode - ADD).
+enum { kHPre0 = 0, kHPre1 = 1, kHPre2 = 2, kHPre3 = 3, kHLeafMem = 4, kHConvert = 5, kHOps = 6, kNumOps = 11 };
 
 struct Compiled {
     ProgramDesc P;
@@ -202,87 +207,180 @@ __device__ __forceinline__ void store_bits(void* p, int bytes, int64_t off, uint
     }
 }
 
-// Four consecutive elements starting at element `off` (aligned access when `vec`).
+// Four consecutive elements starting at element `off` (aligned access when `vec`).  The element
+// type is switched on ONCE per vector, not per element: the evaluator's code size (and with it
+// its instruction-cache behaviour) depends on it.
 template <typename R>
 __device__ __forceinline__ void load_vec4(const void* p, int dt, int64_t off, bool vec, int nvalid, R out[kVec]) {
-    const int bytes = dtype_bytes(dt);
-    uint64_t b[kVec];
-    if (vec && nvalid == kVec) {
-        switch (bytes) {
-            case 1: { uint32_t w = __ldcs(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p) + off));
-                      b[0] = w & 0xff; b[1] = (w >> 8) & 0xff; b[2] = (w >> 16) & 0xff; b[3] = w >> 24; break; }
-            case 2: { uint2 w = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p) + off));
-                      b[0] = w.x & 0xffff; b[1] = w.x >> 16; b[2] = w.y & 0xffff; b[3] = w.y >> 16; break; }
-            case 4: { uint4 w = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const uint32_t*>(p) + off));
-                      b[0] = w.x; b[1] = w.y; b[2] = w.z; b[3] = w.w; break; }
-            default: { const ulonglong2* q = reinterpret_cast<const ulonglong2*>(reinterpret_cast<const uint64_t*>(p) + off);
-                      ulonglong2 w0 = __ldcs(q), w1 = __ldcs(q + 1);
-                      b[0] = w0.x; b[1] = w0.y; b[2] = w1.x; b[3] = w1.y; break; }
+    const bool fast = vec && nvalid == kVec;
+    switch (dt) {
+        case B200_F32: case B200_I32: case B200_U32: {
+            const uint32_t* q = reinterpret_cast<const uint32_t*>(p) + off;
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (fast) w = __ldcs(reinterpret_cast<const uint4*>(q));
+            else {
+                if (0 < nvalid) w.x = __ldcs(q);
+                if (1 < nvalid) w.y = __ldcs(q + 1);
+                if (2 < nvalid) w.z = __ldcs(q + 2);
+                if (3 < nvalid) w.w = __ldcs(q + 3);
+            }
+            out[0] = (R)w.x; out[1] = (R)w.y; out[2] = (R)w.z; out[3] = (R)w.w;
+            break;
         }
-    } else {
+        case B200_F64: case B200_I64: case B200_U64: {
+            const unsigned long long* q = reinterpret_cast<const unsigned long long*>(p) + off;
+            unsigned long long w[kVec] = {0, 0, 0, 0};
+            if (fast) {
+                const ulonglong2 a = __ldcs(reinterpret_cast<const ulonglong2*>(q)), c = __ldcs(reinterpret_cast<const ulonglong2*>(q) + 1);
+                w[0] = a.x; w[1] = a.y; w[2] = c.x; w[3] = c.y;
+            } else {
 #pragma unroll
-        for (int k = 0; k < kVec; ++k) b[k] = (k < nvalid) ? load_bits(p, bytes, off + k) : 0;
+                for (int k = 0; k < kVec; ++k) if (k < nvalid) w[k] = __ldcs(q + k);
+            }
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) out[k] = (R)w[k];
+            break;
+        }
+        case B200_F16: case B200_BF16: case B200_I16: case B200_U16: {
+            const uint16_t* q = reinterpret_cast<const uint16_t*>(p) + off;
+            uint32_t h[kVec] = {0, 0, 0, 0};
+            if (fast) {
+                const uint2 w = __ldcs(reinterpret_cast<const uint2*>(q));
+                h[0] = w.x & 0xffff; h[1] = w.x >> 16; h[2] = w.y & 0xffff; h[3] = w.y >> 16;
+            } else {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) if (k < nvalid) h[k] = __ldcs(q + k);
+            }
+            if (dt == B200_F16) {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) out[k] = raw_of<R>(__half2float(__ushort_as_half((unsigned short)h[k])));
+            } else if (dt == B200_BF16) {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) out[k] = (R)(h[k] << 16);
+            } else if (dt == B200_I16) {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) out[k] = raw_of<R>((int32_t)(int16_t)h[k]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) out[k] = (R)h[k];
+            }
+            break;
+        }
+        default: {
+            const uint8_t* q = reinterpret_cast<const uint8_t*>(p) + off;
+            uint32_t h[kVec] = {0, 0, 0, 0};
+            if (fast) {
+                const uint32_t w = __ldcs(reinterpret_cast<const uint32_t*>(q));
+                h[0] = w & 0xff; h[1] = (w >> 8) & 0xff; h[2] = (w >> 16) & 0xff; h[3] = w >> 24;
+            } else {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) if (k < nvalid) h[k] = __ldcs(q + k);
+            }
+            if (dt == B200_I8) {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) out[k] = raw_of<R>((int32_t)(int8_t)h[k]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) out[k] = (R)h[k];
+            }
+            break;
+        }
     }
-#pragma unroll
-    for (int k = 0; k < kVec; ++k) out[k] = decode<R>(dt, b[k]);
 }
 
 template <typename R>
 __device__ __forceinline__ void store_vec4(void* p, int dt, int64_t off, bool vec, int nvalid, const R in[kVec]) {
-    const int bytes = dtype_bytes(dt);
-    uint64_t b[kVec];
+    const bool fast = vec && nvalid == kVec;
+    switch (dt) {
+        case B200_F32: case B200_I32: case B200_U32: {
+            uint32_t* q = reinterpret_cast<uint32_t*>(p) + off;
+            if (fast) __stcs(reinterpret_cast<uint4*>(q), make_uint4((uint32_t)in[0], (uint32_t)in[1], (uint32_t)in[2], (uint32_t)in[3]));
+            else {
 #pragma unroll
-    for (int k = 0; k < kVec; ++k) b[k] = encode<R>(dt, in[k]);
-    if (vec && nvalid == kVec) {
-        switch (bytes) {
-            case 1: { uint32_t w = (uint32_t)(b[0] & 0xff) | ((uint32_t)(b[1] & 0xff) << 8) | ((uint32_t)(b[2] & 0xff) << 16) | ((uint32_t)(b[3] & 0xff) << 24);
-                      *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p) + off) = w; break; }
-            case 2: { uint2 w; w.x = (uint32_t)(b[0] & 0xffff) | ((uint32_t)(b[1] & 0xffff) << 16);
-                      w.y = (uint32_t)(b[2] & 0xffff) | ((uint32_t)(b[3] & 0xffff) << 16);
-                      __stcs(reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p) + off), w); break; }
-            case 4: { uint4 w = make_uint4((uint32_t)b[0], (uint32_t)b[1], (uint32_t)b[2], (uint32_t)b[3]);
-                      __stcs(reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p) + off), w); break; }
-            default: { ulonglong2* q = reinterpret_cast<ulonglong2*>(reinterpret_cast<uint64_t*>(p) + off);
-                      __stcs(q, make_ulonglong2(b[0], b[1])); __stcs(q + 1, make_ulonglong2(b[2], b[3])); break; }
+                for (int k = 0; k < kVec; ++k) if (k < nvalid) __stcs(q + k, (uint32_t)in[k]);
+            }
+            break;
         }
-    } else {
+        case B200_F64: case B200_I64: case B200_U64: {
+            unsigned long long* q = reinterpret_cast<unsigned long long*>(p) + off;
+            if (fast) {
+                __stcs(reinterpret_cast<ulonglong2*>(q), make_ulonglong2((unsigned long long)in[0], (unsigned long long)in[1]));
+                __stcs(reinterpret_cast<ulonglong2*>(q) + 1, make_ulonglong2((unsigned long long)in[2], (unsigned long long)in[3]));
+            } else {
 #pragma unroll
-        for (int k = 0; k < kVec; ++k) if (k < nvalid) store_bits(p, bytes, off + k, b[k]);
+                for (int k = 0; k < kVec; ++k) if (k < nvalid) __stcs(q + k, (unsigned long long)in[k]);
+            }
+            break;
+        }
+        case B200_F16: case B200_BF16: case B200_I16: case B200_U16: {
+            uint32_t h[kVec];
+            if (dt == B200_F16) {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) h[k] = __half_as_ushort(__float2half_rn(as_c<float>(in[k])));
+            } else if (dt == B200_BF16) {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) h[k] = __bfloat16_as_ushort(__float2bfloat16_rn(as_c<float>(in[k])));
+            } else {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) h[k] = (uint32_t)in[k] & 0xffffu;
+            }
+            uint16_t* q = reinterpret_cast<uint16_t*>(p) + off;
+            if (fast) __stcs(reinterpret_cast<uint2*>(q), make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16)));
+            else {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) if (k < nvalid) q[k] = (uint16_t)h[k];
+            }
+            break;
+        }
+        default: {
+            uint8_t* q = reinterpret_cast<uint8_t*>(p) + off;
+            if (fast) *reinterpret_cast<uint32_t*>(q) = ((uint32_t)in[0] & 0xff) | (((uint32_t)in[1] & 0xff) << 8) | (((uint32_t)in[2] & 0xff) << 16) | (((uint32_t)in[3] & 0xff) << 24);
+            else {
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) if (k < nvalid) q[k] = (uint8_t)in[k];
+            }
+            break;
+        }
     }
 }
 
-// ---- one instruction on statically named stack slots ----------------------------------------------
-// unary: c <- f(c); binary: b <- f(b, c); muladd: a <- a*b+c.  `dt` is the instruction's element
-// type; narrow types are re-rounded / re-wrapped after the operation.
-template <typename C, typename R>
-__device__ __forceinline__ void exec_class(int op, int dt, R* a, R* b, R* c) {
-    using A = Arith<C>;
-    const bool nd = dtype_is_narrow(dt);
-#define B200_CASE(OPC, DST, EXPR)                                   \
-    case OPC:                                                       \
-        _Pragma("unroll") for (int k = 0; k < kVec; ++k) {          \
-            R r = raw_of<R>(EXPR);                                  \
-            if (nd) r = narrow<R>(dt, r);                           \
-            DST[k] = r;                                             \
-        }                                                           \
-        break;
-    switch (op) {
-        B200_CASE(B200_OP_ADD, b, A::add(as_c<C>(b[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_SUB, b, A::sub(as_c<C>(b[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_MUL, b, A::mul(as_c<C>(b[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_DIV, b, A::div(as_c<C>(b[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_MAX, b, A::max(as_c<C>(b[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_MIN, b, A::min(as_c<C>(b[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_MULADD, a, A::muladd(as_c<C>(a[k]), as_c<C>(b[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_ABS, c, A::abs(as_c<C>(c[k])))
-        B200_CASE(B200_OP_ABS2, c, A::mul(as_c<C>(c[k]), as_c<C>(c[k])))
-        B200_CASE(B200_OP_EXP, c, A::exp(as_c<C>(c[k])))
-        B200_CASE(B200_OP_NEG, c, A::neg(as_c<C>(c[k])))
+// Rounds / wraps a whole register vector to a narrow element type (one switch per vector).
+template <typename R>
+__device__ __forceinline__ void narrow_vec(int dt, R v[kVec]) {
+    switch (dt) {
+        case B200_F16:
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) v[k] = raw_of<R>(__half2float(__float2half_rn(as_c<float>(v[k]))));
+            break;
+        case B200_BF16:
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) v[k] = raw_of<R>(__bfloat162float(__float2bfloat16_rn(as_c<float>(v[k]))));
+            break;
+        case B200_I8:
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) v[k] = raw_of<R>((int32_t)(int8_t)as_c<int32_t>(v[k]));
+            break;
+        case B200_I16:
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) v[k] = raw_of<R>((int32_t)(int16_t)as_c<int32_t>(v[k]));
+            break;
+        case B200_U8:
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) v[k] = raw_of<R>(as_c<uint32_t>(v[k]) & 0xffu);
+            break;
+        case B200_U16:
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) v[k] = raw_of<R>(as_c<uint32_t>(v[k]) & 0xffffu);
+            break;
+        case B200_BOOL:
+#pragma unroll
+            for (int k = 0; k < kVec; ++k) v[k] = raw_of<R>(as_c<uint32_t>(v[k]) & 1u);
+            break;
         default: break;
     }
-#undef B200_CASE
 }
 
+// ---- conversions between classes (rare: one nested switch) ---------------------------------------
 template <typename S, typename D, typename R>
 __device__ __forceinline__ void convert_class(R* c) {
 #pragma unroll
@@ -306,42 +404,24 @@ __device__ __forceinline__ void convert_from(int dst_class, R* c) {
 }
 
 template <bool WIDE, typename R>
-__device__ __forceinline__ void exec_instr(int op, int arg, R* a, R* b, R* c) {
-    if (op == B200_OP_CONVERT) {
-        const int src = arg >> 4, dst = arg & 15;
-        const int sc = dtype_class(src), dc = dtype_class(dst);
-        if (sc != dc) {
-            switch (sc) {
-                case CF32: convert_from<float, WIDE>(dc, c); break;
-                case CI32: convert_from<int32_t, WIDE>(dc, c); break;
-                case CU32: convert_from<uint32_t, WIDE>(dc, c); break;
-                default:
-                    if constexpr (WIDE) {
-                        if (sc == CF64) convert_from<double, WIDE>(dc, c);
-                        else if (sc == CI64) convert_from<int64_t, WIDE>(dc, c);
-                        else convert_from<uint64_t, WIDE>(dc, c);
-                    }
-                    break;
-            }
+__device__ __forceinline__ void exec_convert(int arg, R* c) {
+    const int src = arg >> 4, dst = arg & 15;
+    const int sc = dtype_class(src), dc = dtype_class(dst);
+    if (sc != dc) {
+        switch (sc) {
+            case CF32: convert_from<float, WIDE>(dc, c); break;
+            case CI32: convert_from<int32_t, WIDE>(dc, c); break;
+            case CU32: convert_from<uint32_t, WIDE>(dc, c); break;
+            default:
+                if constexpr (WIDE) {
+                    if (sc == CF64) convert_from<double, WIDE>(dc, c);
+                    else if (sc == CI64) convert_from<int64_t, WIDE>(dc, c);
+                    else convert_from<uint64_t, WIDE>(dc, c);
+                }
+                break;
         }
-        if (dtype_is_narrow(dst)) {
-#pragma unroll
-            for (int k = 0; k < kVec; ++k) c[k] = narrow<R>(dst, c[k]);
-        }
-        return;
     }
-    switch (dtype_class(arg)) {
-        case CF32: exec_class<float>(op, arg, a, b, c); break;
-        case CI32: exec_class<int32_t>(op, arg, a, b, c); break;
-        case CU32: exec_class<uint32_t>(op, arg, a, b, c); break;
-        default:
-            if constexpr (WIDE) {
-                if (dtype_class(arg) == CF64) exec_class<double>(op, arg, a, b, c);
-                else if (dtype_class(arg) == CI64) exec_class<int64_t>(op, arg, a, b, c);
-                else exec_class<uint64_t>(op, arg, a, b, c);
-            }
-            break;
-    }
+    if (dtype_is_narrow(dst)) narrow_vec<R>(dst, c);
 }
 
 // Offset of index-space element `lin` inside leaf `L` (general strides / broadcast dims).
@@ -386,46 +466,63 @@ __device__ __forceinline__ void eval_program(const ProgramDesc& P, const int64_t
     for (int k = 0; k < kPrefetch; ++k) {
         if (k < P.nleaves) fetch_leaf<R>(P, k, lin, nvalid, pre[k]);
     }
-    // S[0..2] are never-read placeholders below the stack; the stack proper starts at S[3].
-    R S[kMaxStack + 4][kVec];
-    int sp = 0;
-    for (int pc = 0; pc < P.ninstr; ++pc) {
-        const int op = P.code[2 * pc], arg = P.code[2 * pc + 1];
-        if (op == B200_OP_LEAF) {
-#define B200_PUSH(SLOT)                                                            \
-    {                                                                              \
-        switch (arg) {                                                             \
-            case 0: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[0][j]; break; \
-            case 1: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[1][j]; break; \
-            case 2: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[2][j]; break; \
-            case 3: _Pragma("unroll") for (int j = 0; j < kVec; ++j) S[SLOT][j] = pre[3][j]; break; \
-            default: fetch_leaf<R>(P, arg, lin, nvalid, S[SLOT]); break;           \
-        }                                                                          \
-    }
-            switch (sp) {
-                case 0: B200_PUSH(3) break;
-                case 1: B200_PUSH(4) break;
-                case 2: B200_PUSH(5) break;
-                case 3: B200_PUSH(6) break;
-                default: B200_PUSH(7) break;
-            }
-#undef B200_PUSH
-            ++sp;
-        } else {
-            switch (sp) {
-                case 1: exec_instr<WIDE, R>(op, arg, S[0], S[2], S[3]); break;
-                case 2: exec_instr<WIDE, R>(op, arg, S[2], S[3], S[4]); break;
-                case 3: exec_instr<WIDE, R>(op, arg, S[3], S[4], S[5]); break;
-                case 4: exec_instr<WIDE, R>(op, arg, S[4], S[5], S[6]); break;
-                default: exec_instr<WIDE, R>(op, arg, S[5], S[6], S[7]); break;
-            }
-            if (op == B200_OP_MULADD) sp -= 2;
-            else if (op == B200_OP_ADD || op == B200_OP_SUB || op == B200_OP_MUL || op == B200_OP_DIV ||
-                     op == B200_OP_MAX || op == B200_OP_MIN) sp -= 1;
-        }
-    }
+    // s0 is the top of the stack; a push moves every slot one down, a pop one up
+    R s0[kVec], s1[kVec], s2[kVec], s3[kVec], s4[kVec];
 #pragma unroll
-    for (int j = 0; j < kVec; ++j) result[j] = S[3][j];
+    for (int j = 0; j < kVec; ++j) s0[j] = s1[j] = s2[j] = s3[j] = s4[j] = 0;
+#define B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) { s4[j] = s3[j]; s3[j] = s2[j]; s2[j] = s1[j]; s1[j] = s0[j]; }
+#define B200_POP1() _Pragma("unroll") for (int j = 0; j < kVec; ++j) { s1[j] = s2[j]; s2[j] = s3[j]; s3[j] = s4[j]; }
+#define B200_POP2() _Pragma("unroll") for (int j = 0; j < kVec; ++j) { s1[j] = s3[j]; s2[j] = s4[j]; }
+#define B200_UN(C, EXPR) { _Pragma("unroll") for (int j = 0; j < kVec; ++j) { const C x = as_c<C>(s0[j]); s0[j] = raw_of<R>(EXPR); } } break;
+#define B200_BIN(C, EXPR) { _Pragma("unroll") for (int j = 0; j < kVec; ++j) { const C x = as_c<C>(s1[j]); const C y = as_c<C>(s0[j]); s0[j] = raw_of<R>(EXPR); } B200_POP1() } break;
+#define B200_TER(C, EXPR) { _Pragma("unroll") for (int j = 0; j < kVec; ++j) { const C x = as_c<C>(s2[j]); const C y = as_c<C>(s1[j]); const C z = as_c<C>(s0[j]); s0[j] = raw_of<R>(EXPR); } B200_POP2() } break;
+#define B200_CLASS_CASES(CID, C)                                                          \
+    case kHOps + CID * kNumOps + 0: B200_BIN(C, Arith<C>::add(x, y))                      \
+    case kHOps + CID * kNumOps + 1: B200_BIN(C, Arith<C>::sub(x, y))                      \
+    case kHOps + CID * kNumOps + 2: B200_BIN(C, Arith<C>::mul(x, y))                      \
+    case kHOps + CID * kNumOps + 3: B200_BIN(C, Arith<C>::div(x, y))                      \
+    case kHOps + CID * kNumOps + 4: B200_TER(C, Arith<C>::muladd(x, y, z))                \
+    case kHOps + CID * kNumOps + 5: B200_UN(C, Arith<C>::abs(x))                          \
+    case kHOps + CID * kNumOps + 6: B200_UN(C, Arith<C>::mul(x, x))                       \
+    case kHOps + CID * kNumOps + 7: B200_UN(C, Arith<C>::exp(x))                          \
+    case kHOps + CID * kNumOps + 8: B200_BIN(C, Arith<C>::max(x, y))                      \
+    case kHOps + CID * kNumOps + 9: B200_BIN(C, Arith<C>::min(x, y))                      \
+    case kHOps + CID * kNumOps + 10: B200_UN(C, Arith<C>::neg(x))
+    for (int pc = 0; pc < P.ninstr; ++pc) {
+        const int h = P.hcode[2 * pc], arg = P.hcode[2 * pc + 1];
+        switch (h) {
+            case kHPre0: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[0][j]; break;
+            case kHPre1: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[1][j]; break;
+            case kHPre2: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[2][j]; break;
+            case kHPre3: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[3][j]; break;
+            case kHLeafMem: B200_SHIFT_DOWN() fetch_leaf<R>(P, arg, lin, nvalid, s0); break;
+            case kHConvert: exec_convert<WIDE, R>(arg, s0); break;
+            B200_CLASS_CASES(CF32, float)
+            B200_CLASS_CASES(CI32, int32_t)
+            B200_CLASS_CASES(CU32, uint32_t)
+            default:
+                if constexpr (WIDE) {
+                    switch (h) {
+                        B200_CLASS_CASES(CF64, double)
+                        B200_CLASS_CASES(CI64, int64_t)
+                        B200_CLASS_CASES(CU64, uint64_t)
+                        default: break;
+                    }
+                }
+                break;
+        }
+        // operators on narrow element types re-round / re-wrap their result (operand = that dtype)
+        if (h >= kHOps && arg != 0xff) narrow_vec<R>(arg, s0);
+    }
+#undef B200_CLASS_CASES
+#undef B200_TER
+#undef B200_BIN
+#undef B200_UN
+#undef B200_POP2
+#undef B200_POP1
+#undef B200_SHIFT_DOWN
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) result[j] = s0[j];
 }
 
 #endif  // __CUDACC__
