@@ -275,7 +275,7 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
 
 // ---- device: evaluator kernel -------------------------------------------------------------------------
 template <bool WIDE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, WIDE ? 2 : 3)
 ew_program_kernel(const __grid_constant__ ProgramDesc P, const __grid_constant__ LeafDesc O, int64_t n) {
     using R = typename RawOf<WIDE>::type;
     const int64_t nvec = (n + kVec - 1) / kVec;
