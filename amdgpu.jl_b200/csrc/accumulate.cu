@@ -359,7 +359,6 @@ struct SegPlan {
     int64_t  nsegs;
     int32_t  inclusive, has_init;
     uint32_t max_polls;
-    uint32_t flags;          // bit 0: bulk L2 prefetch of the pass-1 stream, bit 1: early look-back reads
     uint64_t init;
     const void* init_dev;
 };
@@ -633,625 +632,6 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
     if (s_abort && tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
 }
 
-// ---- same protocol, leaner inner loop -------------------------------------------------------------------
-// Differences from the kernel above:
-//  * pass 2 gives every thread 64 CONTIGUOUS bytes of the sub-tile (one serial scan and one warp
-//    scan per sub-tile instead of one warp scan per vector).  The sub-tile is staged in shared
-//    memory warp by warp (each warp copies, scans and writes back its own 2 KiB strip, so only
-//    warp-level synchronisation guards the staging buffers) with the 16-byte slots XOR-swizzled
-//    so that both the coalesced and the thread-contiguous access patterns are conflict free;
-//  * one block barrier per sub-tile (the exchange of the eight warp totals, double buffered);
-//  * the descriptors of the NEXT segment's look-back are read one sub-tile early, two per thread,
-//    so that in the steady state the look-back finds its answer in registers;
-//  * one lane per warp asks L2 for the pass-1 data two sub-tiles ahead with a bulk prefetch,
-//    so that HBM reads do not depend on how many loads the resident warps can keep in flight.
-constexpr int kPrefetchAhead = 2;       // sub-tiles
-constexpr int kLookPerThread = 2;       // look-back descriptors per thread and round
-
-__device__ __forceinline__ int stage_slot(int i) { return i ^ ((i >> 3) & 7); }
-
-template <typename T, int OP>
-__global__ void __launch_bounds__(kSegThreads, 3)
-scan_segment2_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_word) {
-    using Acc = typename ScanAcc<T>::type;
-    constexpr int V = 16 / sizeof(T);
-    constexpr bool kEarlyLook = sizeof(Acc) == 4;       // single-word descriptors can be read ahead
-    using VT = Vec<T, V>;
-    __shared__ __align__(128) uint4 s_stage[2][kSubTileVecs];
-    __shared__ Acc s_tot[2][kSegWarps];
-    __shared__ Acc s_warp[kSegWarps];
-    __shared__ Acc s_prefix, s_total;
-    __shared__ int s_wflag[kSegWarps];
-    __shared__ int s_verdict, s_abort;
-
-    TileState<Acc> state;
-    state.bind(state_mem, pl.nsegs);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint4* src = reinterpret_cast<const uint4*>(A);
-    uint4* dst = reinterpret_cast<uint4*>(B);
-    if (tid == 0) s_abort = 0;
-    __syncthreads();
-    B200_PHASE_BEGIN();
-    const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
-    const int64_t G = gridDim.x;
-    const int per = (int)(pl.seg_vecs / kSubTileVecs);
-
-    auto seed_value = [&]() -> Acc {
-        return (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
-    };
-
-    // Block-wide reduction of the per-thread pass-1 accumulators and publication of the segment's
-    // aggregate (segment 0 publishes its inclusive prefix at once).  Returns the aggregate.
-    auto publish_aggregate = [&](int64_t seg, Acc* acc) -> Acc {
-        Acc r = acc[0];
-#pragma unroll
-        for (int q = 1; q < V; ++q) r = scan_apply<Acc, OP>(r, acc[q]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) r = scan_apply<Acc, OP>(r, __shfl_down_sync(0xffffffffu, r, o));
-        if (lane == 0) s_warp[warp] = r;
-        __syncthreads();
-        if (tid == 0) {
-            Acc t = s_warp[0];
-#pragma unroll
-            for (int w = 1; w < kSegWarps; ++w) t = scan_apply<Acc, OP>(t, s_warp[w]);
-            s_total = t;
-            if (seg == 0) state.publish(0, FLAG_PREFIX, pl.has_init ? scan_apply<Acc, OP>(seed_value(), t) : t);
-            else state.publish(seg, FLAG_AGGREGATE, t);
-        }
-        __syncthreads();
-        const Acc aggregate = s_total;
-        __syncthreads();          // s_total / s_warp may be rewritten right after
-        return aggregate;
-    };
-
-    // Look-back descriptors of one thread: predecessors look - 2*tid (nearest) and look - 2*tid - 1.
-    struct Seen { uint32_t f0, f1; Acc v0, v1; };
-    auto glance = [&](int64_t look, Seen& sn) {
-        const int64_t m0 = look - kLookPerThread * tid, m1 = m0 - 1;
-        sn.f0 = sn.f1 = FLAG_PREFIX;                  // positions before the array end the walk
-        sn.v0 = sn.v1 = scan_identity<Acc, OP>();
-        if (m0 >= 0) sn.f0 = state.peek(m0, sn.v0);
-        if (m1 >= 0) sn.f1 = state.peek(m1, sn.v1);
-    };
-
-    // Block-wide look-back for segment `seg`; `early` holds descriptors read ahead of time when
-    // `have_early`.  Leaves the exclusive prefix in s_prefix and publishes the inclusive one.
-    // False when a wait ran out.
-    auto lookback = [&](int64_t seg, Acc aggregate, const Seen& early, bool have_early) -> bool {
-        if (seg == 0) {
-            if (tid == 0) s_prefix = pl.has_init ? seed_value() : scan_identity<Acc, OP>();
-            __syncthreads();
-            return true;
-        }
-        int64_t look = seg - 1;
-        Acc running = scan_identity<Acc, OP>();
-        bool running_set = false;
-        while (true) {
-            Seen sn;
-            if (have_early) sn = early; else glance(look, sn);
-            have_early = false;
-            const int64_t m0 = look - kLookPerThread * tid, m1 = m0 - 1;
-            bool abort = false;
-            uint32_t polls = 0;
-            while (sn.f0 == FLAG_EMPTY || sn.f1 == FLAG_EMPTY) {
-                ++polls;
-                if (polls > pl.max_polls) { abort = true; break; }
-                if ((polls & 1023u) == 0 && error_latched(err_word)) { abort = true; break; }
-                __nanosleep(polls > 64 ? 512 : 100);
-                if (sn.f0 == FLAG_EMPTY) sn.f0 = state.peek(m0, sn.v0);
-                if (sn.f1 == FLAG_EMPTY) sn.f1 = state.peek(m1, sn.v1);
-            }
-            abort = __any_sync(0xffffffffu, abort);
-            // inside the thread, then inside the warp: the nearest full prefix ends the walk;
-            // everything up to it is combined in array order (farthest first)
-            bool found;
-            Acc contrib;
-            if (sn.f0 == FLAG_PREFIX) { contrib = sn.v0; found = true; }
-            else { contrib = scan_apply<Acc, OP>(sn.v1, sn.v0); found = sn.f1 == FLAG_PREFIX; }
-            const uint32_t pmask = __ballot_sync(0xffffffffu, !abort && found);
-            const int stop = pmask ? (__ffs(pmask) - 1) : 32;
-            if (lane > stop || abort) contrib = scan_identity<Acc, OP>();
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                Acc up = __shfl_down_sync(0xffffffffu, contrib, o);
-                if (lane + o < 32) contrib = scan_apply<Acc, OP>(up, contrib);
-            }
-            if (lane == 0) {
-                s_warp[warp] = contrib;
-                s_wflag[warp] = abort ? 2 : (stop < 32 ? 1 : 0);
-            }
-            __syncthreads();
-            if (tid == 0) {
-                int verdict = 0;
-                for (int w = 0; w < kSegWarps; ++w) {
-                    if (s_wflag[w] == 2) { verdict = 2; break; }
-                    running = running_set ? scan_apply<Acc, OP>(s_warp[w], running) : s_warp[w];
-                    running_set = true;
-                    if (s_wflag[w] == 1) { verdict = 1; break; }
-                }
-                s_verdict = verdict;
-                if (verdict == 1) {
-                    state.publish(seg, FLAG_PREFIX, scan_apply<Acc, OP>(running, aggregate));
-                    s_prefix = running;
-                } else if (verdict == 2) {
-                    s_abort = 1;
-                }
-            }
-            __syncthreads();
-            if (s_verdict != 0) break;
-            look -= kLookPerThread * kSegThreads;
-        }
-        return s_abort == 0;
-    };
-
-    // Bulk L2 prefetch of sub-tile `q` of the pass-1 stream that starts at segment `a` (q may run
-    // past the segment's end: the stream continues with segment a + G).  Lane 0 of each warp asks
-    // for that warp's 2 KiB strip.
-    auto prefetch_stream = [&](int64_t a, int q) {
-        while (q >= per) { q -= per; a += G; }
-        if (lane != 0 || a >= pl.nsegs || !(pl.flags & 1u)) return;
-        const int64_t first = a * pl.seg_vecs + (int64_t)q * kSubTileVecs + warp * (kSubTileVecs / kSegWarps);
-        int64_t count = pl.nvec - first;
-        if (count <= 0) return;
-        if (count > kSubTileVecs / kSegWarps) count = kSubTileVecs / kSegWarps;
-        prefetch_l2_bulk(src + first, (uint32_t)count * 16u, keep);
-    };
-
-    // Pass 1 alone over one segment (prologue only).
-    auto reduce_segment = [&](int64_t seg, Acc* acc) {
-#pragma unroll
-        for (int q = 0; q < V; ++q) acc[q] = scan_identity<Acc, OP>();
-        const int64_t v0 = seg * pl.seg_vecs;
-        const int64_t v1 = (v0 + pl.seg_vecs < pl.nvec) ? v0 + pl.seg_vecs : pl.nvec;
-        for (int64_t base = v0; base < v1; base += kSubTileVecs) {
-            VT v[kScanVecs];
-            bool on[kScanVecs];
-#pragma unroll
-            for (int j = 0; j < kScanVecs; ++j) {
-                const int64_t vi = base + j * kSegThreads + tid;
-                on[j] = vi < v1;
-                if (on[j]) v[j] = __builtin_bit_cast(VT, ld_policy16(src + vi, keep));
-            }
-#pragma unroll
-            for (int j = 0; j < kScanVecs; ++j)
-                if (on[j]) {
-#pragma unroll
-                    for (int q = 0; q < V; ++q) acc[q] = scan_apply<Acc, OP>(acc[q], scan_up<T>(v[j].v[q]));
-                }
-        }
-    };
-
-    // ---- prologue: pass 1 of this block's first two segments.  Aggregates are always published
-    // one whole segment before their prefix is needed, so look-backs find them waiting.
-    int64_t seg = blockIdx.x;
-    if (seg >= pl.nsegs) return;
-#pragma unroll
-    for (int d = 0; d < kPrefetchAhead; ++d) prefetch_stream(seg + 2 * G, d);
-    Acc acc[V];
-    reduce_segment(seg, acc);
-    Acc agg_cur = publish_aggregate(seg, acc);
-    Acc agg_next = scan_identity<Acc, OP>();
-    if (seg + G < pl.nsegs) {
-        reduce_segment(seg + G, acc);
-        agg_next = publish_aggregate(seg + G, acc);
-    }
-    B200_PHASE_MARK(4);   // prologue
-
-    Seen early;
-    early.f0 = early.f1 = FLAG_EMPTY;
-    early.v0 = early.v1 = scan_identity<Acc, OP>();
-    bool have_early = false;
-    const int strip = warp * (kSubTileVecs / kSegWarps);      // first slot of this warp's strip
-    int parity = 0, buf = 0, sub = 0;
-    Acc carry = scan_identity<Acc, OP>();
-    bool seeded = false;
-#pragma unroll
-    for (int q = 0; q < V; ++q) acc[q] = scan_identity<Acc, OP>();
-
-    auto seg_len = [&](int64_t sg) -> int {                   // vectors in segment sg (0 past the end)
-        if (sg >= pl.nsegs) return 0;
-        const int64_t v0 = sg * pl.seg_vecs;
-        return (int)((v0 + pl.seg_vecs < pl.nvec) ? pl.seg_vecs : pl.nvec - v0);
-    };
-    // coalesced copy of this warp's strip of sub-tile `s` of segment `sg` into staging buffer `b`
-    auto stage = [&](int b, int64_t sg, int s) {
-        const int len = seg_len(sg);
-#pragma unroll
-        for (int k = 0; k < kScanVecs; ++k) {
-            const int i = strip + k * 32 + lane;
-            const int off = s * kSubTileVecs + i;
-            if (off < len) cp_async16_policy(&s_stage[b][stage_slot(i)], src + sg * pl.seg_vecs + off, stream);
-        }
-        cp_async_commit();
-    };
-
-    // The block's work is one continuous stream of sub-tiles; the segment events (look-back at a
-    // segment's first sub-tile, aggregate publication after its last) happen with the next
-    // sub-tile's copies and the pass-1 loads already in flight, so the memory pipes never drain.
-    stage(0, seg, 0);
-    while (true) {
-        const int64_t ahead = seg + 2 * G;                 // pass 1 runs two segments ahead
-        const int64_t v0 = seg * pl.seg_vecs, n0 = ahead * pl.seg_vecs;
-        const int len2 = seg_len(seg), len1 = (pl.flags & 8u) ? 0 : seg_len(ahead);   // DIAG
-        const int base = sub * kSubTileVecs;
-        const bool last_sub = sub == per - 1;
-        stage(buf ^ 1, last_sub ? seg + G : seg, last_sub ? 0 : sub + 1);
-        prefetch_stream(ahead, sub + kPrefetchAhead);
-        // loads of pass 1 two segments ahead (L2 is asked to keep the lines for pass 2)
-        VT nxt[kScanVecs];
-#pragma unroll
-        for (int j = 0; j < kScanVecs; ++j)
-            if (base + j * kSegThreads + tid < len1) nxt[j] = __builtin_bit_cast(VT, ld_policy16(src + n0 + base + j * kSegThreads + tid, keep));
-        if (sub == 0) {
-            if (pl.flags & 4u) { if (tid == 0) s_prefix = scan_identity<Acc, OP>(); __syncthreads(); }   // DIAG
-            else
-            if (!lookback(seg, agg_cur, early, have_early)) break;
-            have_early = false;
-            carry = s_prefix;
-            seeded = (seg != 0) || pl.has_init;
-            B200_PHASE_MARK(6);   // look-back
-        }
-        if (kEarlyLook && (pl.flags & 2u) && last_sub && seg + G < pl.nsegs) { glance(seg + G - 1, early); have_early = true; }
-        cp_async_wait<1>();          // this sub-tile's copies (one younger group may be in flight)
-        __syncwarp();
-        // ---- pass 2: serial scan of this thread's 64 bytes, warp scan of the thread totals
-        Acc x[kScanVecs][V];
-#pragma unroll
-        for (int j = 0; j < kScanVecs; ++j) {
-            const int i = 4 * tid + j;
-            const VT c = __builtin_bit_cast(VT, s_stage[buf][stage_slot(i)]);
-            const bool valid = base + i < len2;
-#pragma unroll
-            for (int q = 0; q < V; ++q) x[j][q] = valid ? scan_up<T>(c.v[q]) : scan_identity<Acc, OP>();
-        }
-        Acc run = x[0][0];
-#pragma unroll
-        for (int j = 0; j < kScanVecs; ++j)
-#pragma unroll
-            for (int q = 0; q < V; ++q)
-                if (j + q > 0) { run = scan_apply<Acc, OP>(run, x[j][q]); x[j][q] = run; }
-        const Acc inc = warp_scan_inclusive<Acc, OP>(run, lane);
-        Acc ex = __shfl_up_sync(0xffffffffu, inc, 1);
-        if (lane == 0) ex = scan_identity<Acc, OP>();
-        if (lane == 31) s_tot[parity][warp] = inc;
-        __syncthreads();
-        Acc before = scan_identity<Acc, OP>(), total = scan_identity<Acc, OP>();
-#pragma unroll
-        for (int w = 0; w < kSegWarps; ++w) {
-            const Acc t = s_tot[parity][w];
-            if (w < warp) before = scan_apply<Acc, OP>(before, t);
-            total = scan_apply<Acc, OP>(total, t);
-        }
-        Acc o = scan_apply<Acc, OP>(before, ex);
-        if (seeded) o = scan_apply<Acc, OP>(carry, o);
-#pragma unroll
-        for (int j = 0; j < kScanVecs; ++j) {
-            VT out;
-#pragma unroll
-            for (int q = 0; q < V; ++q) {
-                if (pl.inclusive) out.v[q] = scan_down<T>(scan_apply<Acc, OP>(o, x[j][q]));
-                else if (j + q == 0) out.v[q] = scan_down<T>(o);
-                else out.v[q] = scan_down<T>(scan_apply<Acc, OP>(o, q > 0 ? x[j][q - 1] : x[j > 0 ? j - 1 : 0][V - 1]));
-            }
-            s_stage[buf][stage_slot(4 * tid + j)] = __builtin_bit_cast(uint4, out);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int k = 0; k < kScanVecs; ++k) {
-            const int i = strip + k * 32 + lane;
-            if (base + i < len2) st_policy16(dst + v0 + base + i, s_stage[buf][stage_slot(i)], stream);
-        }
-        __syncwarp();                // the strip is refilled by the copies of the sub-tile after next
-        carry = seeded ? scan_apply<Acc, OP>(carry, total) : total;
-        seeded = true;
-        // ---- pass 1 on the sub-tile of the segment two ahead
-#pragma unroll
-        for (int j = 0; j < kScanVecs; ++j)
-            if (base + j * kSegThreads + tid < len1) {
-#pragma unroll
-                for (int q = 0; q < V; ++q) acc[q] = scan_apply<Acc, OP>(acc[q], scan_up<T>(nxt[j].v[q]));
-            }
-        buf ^= 1;
-        parity ^= 1;
-        if (last_sub) {
-            B200_PHASE_MARK(5);   // fused pass 2 (current) + pass 1 (two ahead)
-            Acc agg_ahead = scan_identity<Acc, OP>();
-            if (ahead < pl.nsegs) agg_ahead = publish_aggregate(ahead, acc);
-#pragma unroll
-            for (int q = 0; q < V; ++q) acc[q] = scan_identity<Acc, OP>();
-            seg += G;
-            if (seg >= pl.nsegs) break;
-            agg_cur = agg_next;
-            agg_next = agg_ahead;
-            sub = 0;
-        } else {
-            ++sub;
-        }
-    }
-    cp_async_wait<0>();
-    if (s_abort && tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
-}
-
-// ---- single-pass ring scan ----------------------------------------------------------------------------
-// Long dense vectors, one HBM read and one HBM write per element, nothing read twice from L2.
-// A block owns every G-th 16 KiB tile (G = one resident wave) and keeps a ring of six tiles in
-// shared memory.  Per step, for its k-th tile, it
-//   1. starts the asynchronous copies of tile k+5 into the slot tile k-1 just left,
-//   2. reduces tile k+3 (its copies were started two steps ago) and publishes that aggregate,
-//   3. finishes the look-back of tile k with descriptors it read two steps ago, then reads the
-//      descriptors for tile k+2 (1024 predecessors, two per thread),
-//   4. scans tile k out of shared memory with the prefix and streams the result out.
-// Aggregates are therefore visible a full step before anybody reads them, descriptor reads have
-// two steps to arrive, and two tiles per block are always in flight from HBM: no wait of the
-// chain (HBM latency, descriptor latency, neighbours' progress) sits in the critical path as long
-// as blocks stay within a step of each other.  A tile resolves as soon as some tile among its
-// 1024 predecessors has published a full prefix; in the steady state that tile is about two
-// waves back.  Every wait is bounded as in the other kernels.
-constexpr int kRingThreads = 512;
-constexpr int kRingWarps = kRingThreads / 32;
-constexpr int kRingTileVecs = 1024;                              // 16 KiB
-constexpr int kRingVecs = kRingTileVecs / kRingThreads;          // 16-byte vectors per thread and tile
-constexpr int kRingAhead = 5;                                    // copies run this many tiles ahead of the scan
-constexpr int kRingReduceAhead = 3;                              // aggregates are published this many tiles ahead
-constexpr int kRingSlots = kRingAhead + 1;
-constexpr int kRingLook = 2;                                     // descriptors per thread and look-back round
-constexpr size_t kRingSmemBytes = (size_t)kRingSlots * kRingTileVecs * 16;
-static_assert(kRingVecs == 2, "thread-contiguous layout below assumes two vectors per thread");
-
-struct RingPlan {
-    int64_t  nvec;           // 16-byte vectors in the whole array
-    int64_t  ntiles;
-    int32_t  inclusive, has_init;
-    uint32_t max_polls;
-    uint64_t init;
-    const void* init_dev;
-};
-
-template <typename T, int OP>
-__global__ void __launch_bounds__(kRingThreads, 2)
-scan_ring_kernel(const T* A, T* B, RingPlan pl, void* state_mem, int32_t* err_word) {
-    using Acc = typename ScanAcc<T>::type;
-    constexpr int V = 16 / sizeof(T);
-    using VT = Vec<T, V>;
-    extern __shared__ __align__(128) uint4 s_ring[];             // [kRingSlots][kRingTileVecs], slots swizzled
-    __shared__ Acc s_red[2][kRingWarps];
-    __shared__ Acc s_tot[2][kRingWarps];
-    __shared__ Acc s_look[kRingWarps];
-    __shared__ int s_lflag[kRingWarps];
-    __shared__ Acc s_agg[kRingSlots];                            // thread 0 only: aggregates of the tiles in the ring
-    __shared__ Acc s_prefix;
-    __shared__ int s_verdict, s_abort;
-
-    TileState<Acc> state;
-    state.bind(state_mem, pl.ntiles);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint4* src = reinterpret_cast<const uint4*>(A);
-    uint4* dst = reinterpret_cast<uint4*>(B);
-    const int64_t G = gridDim.x;
-    const int64_t first = blockIdx.x;
-    if (first >= pl.ntiles) return;
-    const int64_t mine = (pl.ntiles - first + G - 1) / G;        // tiles of this block
-    if (tid == 0) s_abort = 0;
-    __syncthreads();
-    const uint64_t stream = l2_policy_stream();
-    const int strip = warp * (kRingTileVecs / kRingWarps);       // first vector of this warp's 1 KiB strip
-
-    auto seed_value = [&]() -> Acc {
-        return (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
-    };
-    auto tile_len = [&](int64_t g) -> int {                      // vectors in tile g
-        const int64_t left = pl.nvec - g * kRingTileVecs;
-        return left >= kRingTileVecs ? kRingTileVecs : (int)left;
-    };
-
-    // step 1: coalesced asynchronous copy of this warp's strip of the block's k-th tile
-    auto start_copy = [&](int64_t k, int slot) {
-        if (k < mine) {
-            const int64_t g = first + k * G;
-            const int len = tile_len(g);
-#pragma unroll
-            for (int j = 0; j < kRingVecs; ++j) {
-                const int i = strip + j * 32 + lane;
-                if (i < len) cp_async16_policy(&s_ring[slot * kRingTileVecs + stage_slot(i)], src + g * kRingTileVecs + i, stream);
-            }
-        }
-        cp_async_commit();
-    };
-
-    // step 2: block-wide reduction of the k-th tile (already in its slot) and publication
-    int red_parity = 0;
-    auto reduce_publish = [&](int64_t k, int slot) {
-        if (k >= mine) return;
-        const int64_t g = first + k * G;
-        const int len = tile_len(g);
-        Acc r = scan_identity<Acc, OP>();
-#pragma unroll
-        for (int j = 0; j < kRingVecs; ++j) {
-            const int i = kRingVecs * tid + j;
-            if (i < len) {
-                const VT c = __builtin_bit_cast(VT, s_ring[slot * kRingTileVecs + stage_slot(i)]);
-#pragma unroll
-                for (int q = 0; q < V; ++q) r = scan_apply<Acc, OP>(r, scan_up<T>(c.v[q]));
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) r = scan_apply<Acc, OP>(r, __shfl_down_sync(0xffffffffu, r, o));
-        if (lane == 0) s_red[red_parity][warp] = r;
-        __syncthreads();
-        if (tid == 0) {
-            Acc t = s_red[red_parity][0];
-#pragma unroll
-            for (int w = 1; w < kRingWarps; ++w) t = scan_apply<Acc, OP>(t, s_red[red_parity][w]);
-            s_agg[slot] = t;
-            if (g == 0) state.publish(0, FLAG_PREFIX, pl.has_init ? scan_apply<Acc, OP>(seed_value(), t) : t);
-            else state.publish(g, FLAG_AGGREGATE, t);
-        }
-        red_parity ^= 1;
-    };
-
-    // Look-back descriptors of one thread: predecessors look - 2*tid (nearest) and look - 2*tid - 1.
-    struct Seen { uint32_t f0, f1; Acc v0, v1; };
-    auto glance = [&](int64_t look, Seen& sn) {
-        const int64_t m0 = look - kRingLook * tid, m1 = m0 - 1;
-        sn.f0 = sn.f1 = FLAG_PREFIX;                  // positions before the array end the walk
-        sn.v0 = sn.v1 = scan_identity<Acc, OP>();
-        if (m0 >= 0) sn.f0 = state.peek(m0, sn.v0);
-        if (m1 >= 0) sn.f1 = state.peek(m1, sn.v1);
-    };
-
-    // step 3: block-wide look-back for tile g, first round with the descriptors in `early`.
-    // Leaves the exclusive prefix in s_prefix and publishes the inclusive one; false on time-out.
-    auto lookback = [&](int64_t g, int slot, const Seen& early, bool have_early) -> bool {
-        if (g == 0) {
-            if (tid == 0) s_prefix = pl.has_init ? seed_value() : scan_identity<Acc, OP>();
-            __syncthreads();
-            return true;
-        }
-        int64_t look = g - 1;
-        Acc running = scan_identity<Acc, OP>();
-        bool running_set = false;
-        while (true) {
-            Seen sn;
-            if (have_early) sn = early; else glance(look, sn);
-            have_early = false;
-            const int64_t m0 = look - kRingLook * tid, m1 = m0 - 1;
-            bool abort = false;
-            uint32_t polls = 0;
-            while (sn.f0 == FLAG_EMPTY || sn.f1 == FLAG_EMPTY) {
-                ++polls;
-                if (polls > pl.max_polls) { abort = true; break; }
-                if ((polls & 1023u) == 0 && error_latched(err_word)) { abort = true; break; }
-                __nanosleep(polls > 64 ? 512 : 100);
-                if (sn.f0 == FLAG_EMPTY) sn.f0 = state.peek(m0, sn.v0);
-                if (sn.f1 == FLAG_EMPTY) sn.f1 = state.peek(m1, sn.v1);
-            }
-            abort = __any_sync(0xffffffffu, abort);
-            bool found;
-            Acc contrib;
-            if (sn.f0 == FLAG_PREFIX) { contrib = sn.v0; found = true; }
-            else { contrib = scan_apply<Acc, OP>(sn.v1, sn.v0); found = sn.f1 == FLAG_PREFIX; }
-            const uint32_t pmask = __ballot_sync(0xffffffffu, !abort && found);
-            const int stop = pmask ? (__ffs(pmask) - 1) : 32;
-            if (lane > stop || abort) contrib = scan_identity<Acc, OP>();
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                Acc up = __shfl_down_sync(0xffffffffu, contrib, o);
-                if (lane + o < 32) contrib = scan_apply<Acc, OP>(up, contrib);
-            }
-            if (lane == 0) {
-                s_look[warp] = contrib;
-                s_lflag[warp] = abort ? 2 : (stop < 32 ? 1 : 0);
-            }
-            __syncthreads();
-            if (tid == 0) {
-                int verdict = 0;
-                for (int w = 0; w < kRingWarps; ++w) {           // warp 0 holds the nearest predecessors
-                    if (s_lflag[w] == 2) { verdict = 2; break; }
-                    running = running_set ? scan_apply<Acc, OP>(s_look[w], running) : s_look[w];
-                    running_set = true;
-                    if (s_lflag[w] == 1) { verdict = 1; break; }
-                }
-                s_verdict = verdict;
-                if (verdict == 1) {
-                    state.publish(g, FLAG_PREFIX, scan_apply<Acc, OP>(running, s_agg[slot]));
-                    s_prefix = running;
-                } else if (verdict == 2) {
-                    s_abort = 1;
-                }
-            }
-            __syncthreads();
-            if (s_verdict != 0) break;
-            look -= kRingLook * kRingThreads;
-        }
-        return s_abort == 0;
-    };
-
-    // step 4: scan the k-th tile out of its slot and stream it out
-    int tot_parity = 0;
-    auto scan_store = [&](int64_t g, int slot, Acc prefix, bool seeded) {
-        const int len = tile_len(g);
-        uint4* ring = s_ring + slot * kRingTileVecs;
-        Acc x[kRingVecs][V];
-#pragma unroll
-        for (int j = 0; j < kRingVecs; ++j) {
-            const int i = kRingVecs * tid + j;
-            const VT c = __builtin_bit_cast(VT, ring[stage_slot(i)]);
-#pragma unroll
-            for (int q = 0; q < V; ++q) x[j][q] = (i < len) ? scan_up<T>(c.v[q]) : scan_identity<Acc, OP>();
-        }
-        Acc run = x[0][0];
-#pragma unroll
-        for (int j = 0; j < kRingVecs; ++j)
-#pragma unroll
-            for (int q = 0; q < V; ++q)
-                if (j + q > 0) { run = scan_apply<Acc, OP>(run, x[j][q]); x[j][q] = run; }
-        const Acc inc = warp_scan_inclusive<Acc, OP>(run, lane);
-        Acc ex = __shfl_up_sync(0xffffffffu, inc, 1);
-        if (lane == 0) ex = scan_identity<Acc, OP>();
-        if (lane == 31) s_tot[tot_parity][warp] = inc;
-        __syncthreads();
-        // exclusive prefix over the sixteen warp totals, recomputed by every warp
-        const Acc wt = lane < kRingWarps ? s_tot[tot_parity][lane] : scan_identity<Acc, OP>();
-        const Acc winc = warp_scan_inclusive<Acc, OP>(wt, lane);
-        Acc before = __shfl_sync(0xffffffffu, winc, warp > 0 ? warp - 1 : 0);
-        if (warp == 0) before = scan_identity<Acc, OP>();
-        tot_parity ^= 1;
-        Acc o = scan_apply<Acc, OP>(before, ex);
-        if (seeded) o = scan_apply<Acc, OP>(prefix, o);
-#pragma unroll
-        for (int j = 0; j < kRingVecs; ++j) {
-            VT out;
-#pragma unroll
-            for (int q = 0; q < V; ++q) {
-                if (pl.inclusive) out.v[q] = scan_down<T>(scan_apply<Acc, OP>(o, x[j][q]));
-                else if (j + q == 0) out.v[q] = scan_down<T>(o);
-                else out.v[q] = scan_down<T>(scan_apply<Acc, OP>(o, q > 0 ? x[j][q - 1] : x[j > 0 ? j - 1 : 0][V - 1]));
-            }
-            ring[stage_slot(kRingVecs * tid + j)] = __builtin_bit_cast(uint4, out);
-        }
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < kRingVecs; ++j) {
-            const int i = strip + j * 32 + lane;
-            if (i < len) st_policy16(dst + g * kRingTileVecs + i, ring[stage_slot(i)], stream);
-        }
-        __syncwarp();                // the strip is refilled by this warp's next copies
-    };
-
-    // ---- prologue: fill the pipeline
-#pragma unroll
-    for (int k = 0; k < kRingAhead; ++k) start_copy(k, k);
-    // copy groups 0..4 are committed; tile q needs groups 0..q complete
-    cp_async_wait<kRingAhead - 1>(); __syncwarp(); reduce_publish(0, 0);
-    cp_async_wait<kRingAhead - 2>(); __syncwarp(); reduce_publish(1, 1);
-    cp_async_wait<kRingAhead - 3>(); __syncwarp(); reduce_publish(2, 2);
-    static_assert(kRingReduceAhead == 3 && kRingAhead == 5, "prologue is written for this pipeline shape");
-    Seen seen0, seen1;                                            // descriptors for tiles k and k+1
-    bool have0 = false, have1 = false;
-    seen0.f0 = seen0.f1 = seen1.f0 = seen1.f1 = FLAG_EMPTY;
-    seen0.v0 = seen0.v1 = seen1.v0 = seen1.v1 = scan_identity<Acc, OP>();
-
-    int slot = 0;                                                 // slot of tile k
-    for (int64_t k = 0; k < mine; ++k) {
-        const int64_t g = first + k * G;
-        int slot_copy = slot + kRingAhead; if (slot_copy >= kRingSlots) slot_copy -= kRingSlots;
-        int slot_red = slot + kRingReduceAhead; if (slot_red >= kRingSlots) slot_red -= kRingSlots;
-        start_copy(k + kRingAhead, slot_copy);
-        cp_async_wait<kRingAhead - kRingReduceAhead>();           // tile k+3 has landed (two younger groups may fly)
-        __syncwarp();
-        reduce_publish(k + kRingReduceAhead, slot_red);
-        if (!lookback(g, slot, seen0, have0)) break;
-        const Acc prefix = s_prefix;
-        seen0 = seen1; have0 = have1;
-        have1 = false;
-        if (k + 2 < mine) { glance(g + 2 * G - 1, seen1); have1 = true; }
-        scan_store(g, slot, prefix, g != 0 || pl.has_init);
-        if (++slot == kRingSlots) slot = 0;
-    }
-    cp_async_wait<0>();
-    if (s_abort && tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
-}
-
 // One thread per column: sequential walk, coalesced across neighbouring columns when K > 1.
 template <typename T, int OP>
 __global__ void __launch_bounds__(256)
@@ -1289,36 +669,10 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         return B200_OK;
     }
     const bool aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0 && reinterpret_cast<uintptr_t>(B) % 16 == 0;
-    static const int variant = getenv("B200_SCAN_VARIANT") ? atoi(getenv("B200_SCAN_VARIANT")) : 1;
-    if (variant == 3 && ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {
-        RingPlan rp{};
-        rp.nvec = pl.L * (int64_t)sizeof(T) / 16;
-        rp.ntiles = (rp.nvec + kRingTileVecs - 1) / kRingTileVecs;
-        rp.inclusive = pl.inclusive;
-        rp.has_init = pl.has_init;
-        rp.max_polls = pl.max_polls;
-        rp.init = pl.init;
-        rp.init_dev = pl.init_dev;
-        auto kernel = scan_ring_kernel<T, OP>;
-        B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRingSmemBytes));
-        // exactly one resident wave: blocks wait for descriptors of blocks that have to be running
-        int64_t grid = resident_blocks(kernel, kRingThreads, kRingSmemBytes, st->dev);
-        if (grid > rp.ntiles) grid = rp.ntiles;
-        void* scr = nullptr;
-        unsigned int* counters = nullptr;
-        const size_t sbytes = TileState<Acc>::bytes(rp.ntiles);
-        B200_TRY(scratch(st, sbytes, &scr, &counters));
-        B200_CUDA(cudaMemsetAsync(scr, 0, sbytes, st->s));
-        kernel<<<(unsigned)grid, kRingThreads, kRingSmemBytes, st->s>>>((const T*)A, (T*)B, rp, scr, device_error_word(st->dev));
-        return B200_OK;
-    }
     if (ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {
         SegPlan sp{};
         sp.nvec = pl.L * (int64_t)sizeof(T) / 16;
-        // the grid must be exactly one resident wave: blocks wait for descriptors of blocks that
-        // have to be running
-        int64_t grid = variant == 1 ? resident_blocks(scan_segment_kernel<T, OP>, kSegThreads, 0, st->dev)
-                                    : resident_blocks(scan_segment2_kernel<T, OP>, kSegThreads, 0, st->dev);
+        int64_t grid = resident_blocks(scan_segment_kernel<T, OP>, kSegThreads, 0, st->dev);
         // segments are whole sub-tiles of 16 KiB: 48 KiB measured best for long vectors (look-backs
         // are rare enough and the live segments of all blocks stay far below the L2 capacity)
         const int64_t subv = kSubTileVecs;
@@ -1331,8 +685,6 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         sp.inclusive = pl.inclusive;
         sp.has_init = pl.has_init;
         sp.max_polls = pl.max_polls;
-        static const uint32_t seg_flags = getenv("B200_SCAN_FLAGS") ? (uint32_t)atoi(getenv("B200_SCAN_FLAGS")) : 3u;
-        sp.flags = seg_flags;
         sp.init = pl.init;
         sp.init_dev = pl.init_dev;
         void* scr = nullptr;
@@ -1341,10 +693,7 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         B200_TRY(scratch(st, sbytes, &scr, &counters));
         B200_CUDA(cudaMemsetAsync(scr, 0, sbytes, st->s));
         if (grid > sp.nsegs) grid = sp.nsegs;
-        if (variant == 1)
-            scan_segment_kernel<T, OP><<<(unsigned)grid, kSegThreads, 0, st->s>>>((const T*)A, (T*)B, sp, scr, device_error_word(st->dev));
-        else
-            scan_segment2_kernel<T, OP><<<(unsigned)grid, kSegThreads, 0, st->s>>>((const T*)A, (T*)B, sp, scr, device_error_word(st->dev));
+        scan_segment_kernel<T, OP><<<(unsigned)grid, kSegThreads, 0, st->s>>>((const T*)A, (T*)B, sp, scr, device_error_word(st->dev));
         return B200_OK;
     }
     pl.tiles_per_col = (pl.L + TILE - 1) / TILE;

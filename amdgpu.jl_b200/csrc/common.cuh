@@ -170,12 +170,6 @@ __device__ __forceinline__ void st_policy16(uint4* ptr, uint4 v, uint64_t policy
                  ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(policy) : "memory");
 }
 
-// Asks L2 to fetch `bytes` (a multiple of 16, 16-byte aligned start) ahead of use; one instruction,
-// no register or shared-memory destination.
-__device__ __forceinline__ void prefetch_l2_bulk(const void* ptr, uint32_t bytes, uint64_t policy) {
-    asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(ptr), "r"(bytes), "l"(policy) : "memory");
-}
-
 // 16-byte asynchronous copy global -> shared (bypasses registers and L1), grouped by commit/wait.
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
