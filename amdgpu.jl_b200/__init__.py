@@ -21,7 +21,7 @@ from .mapreduce import prepared as mapreduce_prepared
 from .accumulate import accumulate_, accumulate, cumsum, cumprod
 from .accumulate import prepared as accumulate_prepared
 from .sorting import sort_, sort, sortperm_, sortperm
-from .indexing import findall, getindex_mask, reverse, reverse_
+from .indexing import findall, getindex, getindex_mask, reverse, reverse_
 from . import random
 from . import sharded
 

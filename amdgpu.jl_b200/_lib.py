@@ -142,6 +142,7 @@ SIGNATURES = {
     "b200_sortperm": [_vp, _P(Tensor), _P(Tensor), _i32],
     "b200_compact": [_vp, _P(Tensor), _P(Tensor), _P(Tensor), _P(Tensor)],
     "b200_reverse": [_vp, _P(Tensor), _P(Tensor), C.c_uint32],
+    "b200_gather": [_vp, _P(Tensor), _P(Tensor), _P(Tensor)],
     "b200_fill_random": [_vp, _P(Tensor), _i32, _u64, _u64, _u64, _i64, _i64],
     "b200_selftest_wait_timeout": [_vp, C.c_uint32],
     "b200_peer_create": [_i32, _i32, _i32, _P(_vp), C.c_char_p],

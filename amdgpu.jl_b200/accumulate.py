@@ -12,7 +12,7 @@ import ctypes as C
 import numpy as np
 
 from ._lib import check, lib
-from .array import ROCArray
+from .array import ROCArray, copyto_
 from .mapreduce import _op_code
 from .runtime import Stream, current_stream
 
@@ -34,9 +34,14 @@ def accumulate_(op, B: ROCArray, A: ROCArray, init=_ZERO, dims=None, inclusive: 
     if init is _ZERO:
         init = A.dtype.type(0)
     init_buf = None if init is None else np.asarray(init, dtype=A.dtype).tobytes()
-    tb, ta = B.tensor(), A.tensor()
+    # the scan kernels want dense operands: wrapped ones (views, permuted dims) go through a dense
+    # temporary, one strided copy in and one out
+    Ad, Bd = A.dense(), (B if B.is_contiguous else B.similar())
+    tb, ta = Bd.tensor(), Ad.tensor()
     check(lib.b200_accumulate((stream or current_stream()).handle, C.byref(tb), C.byref(ta), _op_code(op),
                               init_buf, dims - 1, 1 if inclusive else 0))
+    if Bd is not B:
+        copyto_(B, Bd, stream)
     return B
 
 

@@ -48,8 +48,12 @@ class _Managed:
 class ROCArray:
     __array_ufunc__ = None      # never let NumPy treat a device array as an object scalar
 
-    def __init__(self, dtype, dims, *, _buf: _Managed | None = None, _offset: int = 0, stream: Stream | None = None):
-        """``ROCArray{T}(undef, dims)`` (src/array.jl:24-32): uninitialised storage from the pool."""
+    def __init__(self, dtype, dims, *, _buf: _Managed | None = None, _offset: int = 0, _strides=None,
+                 stream: Stream | None = None):
+        """``ROCArray{T}(undef, dims)`` (src/array.jl:24-32): uninitialised storage from the pool.
+        With `_strides` (element strides) the object stands for one of the reference's wrapped
+        arrays over the same buffer: ``SubArray``, ``PermutedDimsArray``, ``Transpose``
+        (``AnyROCArray``, src/array.jl:138-147)."""
         self.dtype = np.dtype(dtype)
         _lib.dtype_code(self.dtype)
         if isinstance(dims, (int, np.integer)):
@@ -63,6 +67,9 @@ class ROCArray:
             _buf = _Managed(self.nbytes, stream or current_stream())
         self.buf = _buf
         self.offset = _offset
+        self._strides = None if _strides is None else tuple(int(x) for x in _strides)
+        if self._strides is not None and self._strides == self._dense_strides():
+            self._strides = None
 
     # ---- basic properties
     @property
@@ -81,13 +88,25 @@ class ROCArray:
         if self.buf.freed:
             raise RuntimeError("use of a ROCArray after unsafe_free!")
         return (self.buf.ptr + self.offset) if self.size else 0
-    @property
-    def strides(self):
+    def _dense_strides(self):
         s, acc = [], 1
         for d in self.dims:
             s.append(acc)
             acc *= d
         return tuple(s)
+    @property
+    def strides(self):
+        """Element strides, column-major (``strides(A)``)."""
+        return self._dense_strides() if self._strides is None else self._strides
+    @property
+    def is_contiguous(self) -> bool:
+        """True for a dense column-major array (dimensions of extent 1 may carry any stride)."""
+        if self._strides is None:
+            return True
+        return all(d == 1 or a == b for d, a, b in zip(self.dims, self._strides, self._dense_strides()))
+    def dense(self) -> "ROCArray":
+        """`self` if it is dense, else a dense copy (what the reference gets from ``copy`` of a view)."""
+        return self if self.is_contiguous else self.copy()
     @property
     def device(self) -> int: return self.buf.stream.device
 
@@ -117,6 +136,9 @@ class ROCArray:
         a = np.asarray(a, dtype=self.dtype)
         if a.size != self.size:
             raise ValueError("size mismatch in copyto!")
+        if not self.is_contiguous:          # upload densely, then one strided device copy
+            copyto_(self, ROCArray.from_host(a.reshape(self.dims, order="F"), stream), stream)
+            return self
         flat = np.ascontiguousarray(a.reshape(-1, order="F"))
         st = stream or current_stream()
         if flat.nbytes:
@@ -126,6 +148,8 @@ class ROCArray:
 
     def to_host(self, stream: Stream | None = None) -> np.ndarray:
         """``Array(x::ROCArray)`` (src/array.jl:215-227): blocking download."""
+        if not self.is_contiguous:
+            return self.copy().to_host(stream)
         out = np.empty(self.size, dtype=self.dtype)
         st = stream or current_stream()
         if out.nbytes:
@@ -155,6 +179,8 @@ class ROCArray:
             dims = tuple(dims[0])
         if math.prod(dims) != self.size:
             raise ValueError("reshape: total size must not change")
+        if not self.is_contiguous:
+            raise ValueError("reshape of a strided view: copy it first")
         return ROCArray(self.dtype, dims, _buf=self.buf, _offset=self.offset)
 
     def view(self, start: int, stop: int) -> "ROCArray":
@@ -162,16 +188,74 @@ class ROCArray:
         pointer is ``base + offset`` and need not be 16-byte aligned (src/array.jl:353-354)."""
         if not 0 <= start <= stop <= self.size:
             raise IndexError("view out of range")
+        if not self.is_contiguous:
+            raise ValueError("linear view of a strided view: copy it first")
         return ROCArray(self.dtype, (stop - start,), _buf=self.buf, _offset=self.offset + start * self.itemsize)
+
+    def subview(self, *index) -> "ROCArray":
+        """``@view A[i1, i2, ...]`` with one entry per dimension (``StridedSubROCArray``,
+        src/array.jl:138-141; test/core/rocarray_base.jl:55-62).  Entries are 0-based Python
+        slices (a positive step is allowed) or integers; an integer drops its dimension, as a
+        scalar index does in Julia.  The result shares the buffer."""
+        if len(index) != self.ndim:
+            raise IndexError("subview needs one index per dimension")
+        off, dims, strides = self.offset, [], []
+        for ix, d, st in zip(index, self.dims, self.strides):
+            if isinstance(ix, (int, np.integer)):
+                if not 0 <= ix < d:
+                    raise IndexError("subview index out of range")
+                off += int(ix) * st * self.itemsize
+                continue
+            if not isinstance(ix, slice):
+                raise TypeError("subview takes slices and integers")
+            lo, hi, step = ix.indices(d)
+            if step <= 0:
+                raise ValueError("subview needs a positive step")
+            n = max(0, (hi - lo + step - 1) // step)
+            off += lo * st * self.itemsize if n else 0
+            dims.append(n)
+            strides.append(st * step)
+        return ROCArray(self.dtype, tuple(dims), _buf=self.buf, _offset=off, _strides=tuple(strides))
+
+    def permuteddims(self, perm) -> "ROCArray":
+        """``PermutedDimsArray(A, perm)``: lazy, shares the buffer; `perm` is 1-based."""
+        perm = tuple(int(p) for p in perm)
+        if sorted(perm) != list(range(1, self.ndim + 1)):
+            raise ValueError("perm must be a permutation of 1:ndims")
+        st = self.strides
+        return ROCArray(self.dtype, tuple(self.dims[p - 1] for p in perm), _buf=self.buf, _offset=self.offset,
+                        _strides=tuple(st[p - 1] for p in perm))
+
+    def transpose(self) -> "ROCArray":
+        """``transpose(A)`` (lazy, like ``LinearAlgebra.Transpose``); a vector becomes a 1xN row.
+        For the real element types of this path ``adjoint`` is the same thing."""
+        if self.ndim == 1:
+            return ROCArray(self.dtype, (1, self.dims[0]), _buf=self.buf, _offset=self.offset,
+                            _strides=(1, self.strides[0]))
+        if self.ndim != 2:
+            raise ValueError("transpose needs a vector or a matrix")
+        return self.permuteddims((2, 1))
+
+    adjoint = transpose
+
+    def permutedims(self, perm) -> "ROCArray":
+        """``permutedims(A, perm)``: dense result."""
+        return self.permuteddims(perm).copy()
 
     def reinterpret(self, dtype) -> "ROCArray":
         dtype = np.dtype(dtype)
+        if not self.is_contiguous:
+            raise ValueError("reinterpret of a strided view: copy it first")
         if self.nbytes % dtype.itemsize:
             raise ValueError("reinterpret: size is not a multiple of the new element size")
         return ROCArray(dtype, (self.nbytes // dtype.itemsize,), _buf=self.buf, _offset=self.offset)
 
     def fill_(self, value, stream: Stream | None = None) -> "ROCArray":
         """``fill!(A, x)`` as a bit-pattern memset (src/array.jl:253-266)."""
+        if self.size and not self.is_contiguous:
+            from .broadcast import Broadcasted, materialize_
+            materialize_(self, Broadcasted.leaf(self.dtype.type(value)), stream)
+            return self
         if self.size:
             bits = int.from_bytes(np.asarray(value, dtype=self.dtype).tobytes().ljust(8, b"\0"), "little")
             check(lib.b200_memset_async(C.c_void_p(self.ptr), bits, self.itemsize, self.size,
@@ -196,6 +280,13 @@ def copyto_(dest: ROCArray, src: ROCArray, stream: Stream | None = None) -> ROCA
     """Device-to-device ``copyto!`` (src/array.jl:240-249)."""
     if dest.size != src.size or dest.dtype != src.dtype:
         raise ValueError("copyto!: size or element type mismatch")
+    if dest.size and not (dest.is_contiguous and src.is_contiguous):
+        # wrapped operands: one pass of the broadcast kernel with the strides in the descriptors
+        if dest.dims != src.dims:
+            raise ValueError("copyto! between strided arrays needs equal shapes")
+        from .broadcast import Broadcasted, materialize_
+        materialize_(dest, Broadcasted.leaf(src), stream)
+        return dest
     if dest.size:
         check(lib.b200_memcpy_async(C.c_void_p(dest.ptr), C.c_void_p(src.ptr), src.nbytes,
                                     (stream or current_stream()).handle))

@@ -46,9 +46,55 @@ __global__ void __launch_bounds__(256) reverse_kernel(void* y, const void* x, Fl
     }
 }
 
+// y[i] = x[ix[i]] with 1-based indices (Int64 or Int32).  An index outside 1..nx latches
+// B200_INVALID_ARG in the device's error word (reported by the next synchronisation, like the
+// reference's asynchronous BoundsError) and leaves that output element untouched.
+template <int BYTES, typename IT>
+__global__ void __launch_bounds__(256)
+gather_kernel(void* y, const void* x, const IT* ix, int64_t n, int64_t nx, int32_t* err_word) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t j = (int64_t)ix[i] - 1;
+        if (j < 0 || j >= nx) { latch_error(err_word, B200_INVALID_ARG); continue; }
+        store_bits(y, BYTES, i, load_bits(x, BYTES, j));
+    }
+}
+
+template <typename IT>
+static void launch_gather(b200_stream_t st, const b200_tensor* y, const b200_tensor* x, const b200_tensor* ix, int64_t n) {
+    const unsigned grid = balanced_grid((n + 255) / 256, (int64_t)sm_count(st->dev) * 8);
+    const IT* idx = reinterpret_cast<const IT*>(ix->ptr);
+    const int64_t nx = tensor_numel(x);
+    int32_t* err = device_error_word(st->dev);
+    switch (dtype_size(x->dtype)) {
+        case 1: gather_kernel<1, IT><<<grid, 256, 0, st->s>>>(y->ptr, x->ptr, idx, n, nx, err); break;
+        case 2: gather_kernel<2, IT><<<grid, 256, 0, st->s>>>(y->ptr, x->ptr, idx, n, nx, err); break;
+        case 4: gather_kernel<4, IT><<<grid, 256, 0, st->s>>>(y->ptr, x->ptr, idx, n, nx, err); break;
+        default: gather_kernel<8, IT><<<grid, 256, 0, st->s>>>(y->ptr, x->ptr, idx, n, nx, err); break;
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int32_t b200_gather(b200_stream_t st, const b200_tensor* y, const b200_tensor* x, const b200_tensor* ix) {
+    B200_TRY(enter(st));
+    B200_TRY(check_tensor(y, "gather destination"));
+    B200_TRY(check_tensor(x, "gather source"));
+    B200_TRY(check_tensor(ix, "gather indices"));
+    if (x->dtype != y->dtype) return fail(B200_INVALID_ARG, "gather: source and destination differ in element type");
+    if (ix->dtype != B200_I64 && ix->dtype != B200_I32) return fail(B200_UNSUPPORTED, "gather: indices must be Int64 or Int32");
+    if (!tensor_is_contiguous(x) || !tensor_is_contiguous(y) || !tensor_is_contiguous(ix))
+        return fail(B200_UNSUPPORTED, "gather: operands must be dense");
+    const int64_t n = tensor_numel(ix);
+    if (tensor_numel(y) != n) return fail(B200_INVALID_ARG, "gather: destination and indices differ in length");
+    if (n == 0) return B200_OK;
+    if (tensor_numel(x) == 0) return fail(B200_INVALID_ARG, "gather: indexing into an empty array");
+    if (ix->dtype == B200_I64) launch_gather<int64_t>(st, y, x, ix, n);
+    else launch_gather<int32_t>(st, y, x, ix, n);
+    return finish(st, "b200_gather");
+}
 
 extern "C" int32_t b200_compact(b200_stream_t st, const b200_tensor* ys, const b200_tensor* bools,
                                 const b200_tensor* indices, const b200_tensor* values) {

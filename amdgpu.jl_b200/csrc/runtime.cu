@@ -300,8 +300,11 @@ static int32_t check_latched(DeviceState* d) {
     int32_t code = *(volatile int32_t*)d->err_host;
     if (code != 0) {
         *(volatile int32_t*)d->err_host = 0;
-        return fail(code, "a device-side wait ran out of its poll budget (%s); the result of the "
-                          "operation that reported it is invalid", b200_status_name(code));
+        if (code == B200_LOOKBACK_TIMEOUT)
+            return fail(code, "a device-side wait ran out of its poll budget (%s); the result of the "
+                              "operation that reported it is invalid", b200_status_name(code));
+        return fail(code, "a kernel reported %s (for example an index outside its array); the result of "
+                          "the operation that reported it is incomplete", b200_status_name(code));
     }
     return B200_OK;
 }

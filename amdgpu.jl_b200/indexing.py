@@ -58,6 +58,20 @@ def getindex_mask(xs: ROCArray, bools: ROCArray, stream: Stream | None = None) -
     return ys
 
 
+def getindex(xs: ROCArray, ix: ROCArray, stream: Stream | None = None) -> ROCArray:
+    """``xs[ix]`` with a device vector of 1-based integer indices (the vectorised ``getindex`` the
+    reference's sorting tests use, test/hip_rocarray/sorting.jl:14).  `xs` is indexed linearly;
+    an out-of-range index surfaces as an error at the next synchronisation."""
+    if ix.dtype not in (np.dtype(np.int64), np.dtype(np.int32)):
+        raise ValueError("index vectors must be Int64 or Int32")
+    st = stream or current_stream()
+    xd, ixd = xs.dense(), ix.dense()
+    out = ROCArray(xs.dtype, ix.dims, stream=st)
+    ty, tx, ti = out.tensor(), xd.tensor(), ixd.tensor()
+    check(lib.b200_gather(st.handle, C.byref(ty), C.byref(tx), C.byref(ti)))
+    return out
+
+
 def _mask(x: ROCArray, dims) -> int:
     if dims is None:
         dims = range(1, x.ndim + 1)

@@ -239,6 +239,11 @@ int32_t b200_sortperm(b200_stream_t st, const b200_tensor* ix, const b200_tensor
  * receives the 1-based linear indices of the true entries; otherwise ys receives values[mask]. */
 int32_t b200_compact(b200_stream_t st, const b200_tensor* ys, const b200_tensor* bools,
                      const b200_tensor* indices, const b200_tensor* values);
+/* replaces getindex with an integer index vector, y = x[ix] (GPUArrays' vectorised getindex, as
+ * used by test/hip_rocarray/sorting.jl:14 `xd[sortperm(xd)]`): indices are 1-based Int64 or Int32,
+ * x is read in linear order whatever its shape.  An index outside 1..length(x) latches
+ * B200_INVALID_ARG, reported by the next b200_stream_sync; that output element is not written. */
+int32_t b200_gather(b200_stream_t st, const b200_tensor* y, const b200_tensor* x, const b200_tensor* ix);
 /* replaces _reverse! (src/kernels/reverse.jl:59-87): y = x flipped along the dimensions whose bit
  * is set in dims_mask (bit 0 = first dimension); y and x must not alias. */
 int32_t b200_reverse(b200_stream_t st, const b200_tensor* y, const b200_tensor* x, uint32_t dims_mask);

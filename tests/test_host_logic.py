@@ -51,6 +51,46 @@ def test_scalar_leaf_types(pkg):
         B.call("sin", 1.0)
 
 
-def test_sort_rejects_closures(pkg):
+def test_sort_order_keywords(pkg):
+    order = pkg.sorting._order
+    assert order(False, None) is False and order(True, None) is True
+    assert order(False, "<") is False and order(False, ">") is True and order(False, "!isless") is True
+    assert order(True, ">") is False                  # reversed twice
     with pytest.raises(ValueError):
-        pkg.sorting._check_kwargs(lt=lambda a, b: a > b, by=None)
+        order(False, lambda a, b: a > b)              # closures cannot run inside a radix sort
+    with pytest.raises(ValueError):
+        order(False, ">=")
+
+
+class _FakeBuffer:
+    """Stands in for pool memory so that view geometry can be checked without a device."""
+    ptr, freed, stream = 1 << 20, False, None
+
+
+def test_view_geometry_matches_numpy(pkg):
+    shape = (6, 5, 4)
+    host = np.asfortranarray(np.arange(np.prod(shape), dtype=np.float32).reshape(shape, order="F"))
+    A = pkg.ROCArray(np.float32, shape, _buf=_FakeBuffer())
+    assert A.is_contiguous and A.strides == (1, 6, 30)
+
+    def same(view, ref):
+        assert view.dims == ref.shape
+        assert view.strides == tuple(s // 4 for s in ref.strides)
+        assert view.ptr - A.ptr == ref.__array_interface__["data"][0] - host.__array_interface__["data"][0]
+
+    same(A.subview(slice(1, 5), slice(None), slice(None)), host[1:5])
+    same(A.subview(slice(0, 6, 2), 3, slice(1, 4)), host[0:6:2, 3, 1:4])
+    same(A.subview(2, slice(None), 1), host[2, :, 1])
+    same(A.permuteddims((3, 1, 2)), host.transpose(2, 0, 1))
+    M = A.subview(slice(None), slice(None), 0)
+    same(M.transpose(), host[:, :, 0].T)
+    assert not M.transpose().is_contiguous and M.is_contiguous
+    assert A.subview(slice(None), slice(None), slice(0, 1)).is_contiguous       # extent-1 dims do not matter
+    row = pkg.ROCArray(np.float32, (7,), _buf=_FakeBuffer()).transpose()
+    assert row.dims == (1, 7) and row.is_contiguous
+    with pytest.raises(ValueError):
+        A.subview(slice(0, 6, 2), slice(None), slice(None)).reshape(60)
+    with pytest.raises(IndexError):
+        A.subview(6, slice(None), slice(None))
+    with pytest.raises(ValueError):
+        A.permuteddims((1, 1, 2))
