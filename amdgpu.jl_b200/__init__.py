@@ -12,7 +12,8 @@ from .runtime import (Stream, Event, elapsed_ms, elapsed, ndevices, devices, cur
                       current_stream, stream_, using_stream, priority_, synchronize, device_synchronize,
                       device_properties, can_access_peer, versioninfo, functional)
 from .memory import (mem_info, parse_memory_limit, configure, reclaim, reclaim_hook, pool_alloc, pool_free,
-                     pool_stats, used_memory, cached_memory)
+                     pool_stats, used_memory, cached_memory, AllocCache, cached, PoolCleanup,
+                     start_pool_cleanup)
 from .array import ROCArray, copyto_, zeros, ones, fill, roc
 from . import broadcast
 from .broadcast import Broadcasted, materialize_, promote_type
@@ -23,6 +24,8 @@ from .accumulate import prepared as accumulate_prepared
 from .sorting import sort_, sort, sortperm_, sortperm
 from .indexing import findall, getindex, getindex_mask, reverse, reverse_
 from . import random
+from . import graph
+from .graph import Graph, GraphExec, capture, instantiate, launch, update, is_capturing, captured
 from . import sharded
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -143,6 +143,14 @@ SIGNATURES = {
     "b200_compact": [_vp, _P(Tensor), _P(Tensor), _P(Tensor), _P(Tensor)],
     "b200_reverse": [_vp, _P(Tensor), _P(Tensor), C.c_uint32],
     "b200_gather": [_vp, _P(Tensor), _P(Tensor), _P(Tensor)],
+    "b200_graph_capture_begin": [_vp, C.c_int32],
+    "b200_graph_capture_end": [_vp, _P(_vp)],
+    "b200_stream_is_capturing": [_vp, _P(C.c_int32)],
+    "b200_graph_destroy": [_vp],
+    "b200_graph_instantiate": [_vp, _P(_vp)],
+    "b200_graph_exec_destroy": [_vp],
+    "b200_graph_launch": [_vp, _vp],
+    "b200_graph_exec_update": [_vp, _vp, _P(C.c_int32)],
     "b200_fill_random": [_vp, _P(Tensor), _i32, _u64, _u64, _u64, _i64, _i64],
     "b200_selftest_wait_timeout": [_vp, C.c_uint32],
     "b200_peer_create": [_i32, _i32, _i32, _P(_vp), C.c_char_p],

@@ -15,7 +15,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import check, lib
-from .memory import pool_alloc, pool_free
+from .memory import current_cache, pool_alloc, pool_free
 from .runtime import Stream, current_stream
 
 
@@ -23,16 +23,24 @@ class _Managed:
     """Reference-counted device buffer tied to the stream that owns it (the role of
     ``Managed`` + ``DataRef``, src/memory.jl:408-418)."""
 
-    __slots__ = ("ptr", "nbytes", "stream", "freed", "__weakref__")
+    __slots__ = ("ptr", "nbytes", "stream", "freed", "cached", "__weakref__")
 
     def __init__(self, nbytes: int, stream: Stream):
         self.ptr, self.freed = 0, True          # a failed allocation must leave a harmless object
         self.nbytes = nbytes
         self.stream = stream
-        self.ptr = pool_alloc(nbytes, stream)
+        cache = current_cache()                 # GPUArrays.cached_alloc hook (src/array.jl:27-30)
+        self.cached = cache is not None and nbytes > 0
+        if self.cached:
+            self.ptr = cache.take((stream.device, nbytes), lambda: pool_alloc(nbytes, stream))
+        else:
+            self.ptr = pool_alloc(nbytes, stream)
         self.freed = False
 
     def free(self) -> None:
+        if self.cached:                         # the allocation cache owns the memory
+            self.freed = True
+            return
         if not self.freed and self.ptr:
             self.freed = True
             try:

@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <stddef.h>
 #include <string>
+#include <vector>
 
 #include "../../include/b200arrays.h"
 
@@ -19,6 +20,11 @@ struct b200_stream_s {
     // buffer per stream can be reused by every call without extra synchronisation.
     void*        scratch;
     size_t       scratch_bytes;
+    // A captured graph keeps the scratch address it saw: once an operator asked for scratch
+    // during a capture the buffer is never freed while the stream lives (it moves to `retired`
+    // if a later call needs a larger one).
+    bool         scratch_in_graph;
+    std::vector<void*> retired;
 };
 
 struct b200_event_s {

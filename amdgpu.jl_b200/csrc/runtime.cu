@@ -111,7 +111,10 @@ int sm_count(int dev) { return g_dev[dev]->sms; }
 int32_t finish(b200_stream_t st, const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, what);
-    if (g_launch_blocking) return b200_stream_sync(st);
+    if (g_launch_blocking) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st->s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) return b200_stream_sync(st);
+    }
     return B200_OK;
 }
 
@@ -154,16 +157,27 @@ int32_t scratch(b200_stream_t st, size_t bytes, void** out, unsigned int** count
     DeviceState* d;
     B200_TRY(device_state(st->dev, &d));
     const size_t need = bytes + kCounterBytes;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    B200_CUDA(cudaStreamIsCapturing(st->s, &cap));
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
     if (need > st->scratch_bytes) {
+        // growing would put an allocation and a zero-fill of the counters into the graph and leave
+        // the stream with an address that only exists inside that graph
+        if (capturing)
+            return fail(B200_UNSUPPORTED, "this operation needs %zu bytes of stream scratch and the stream holds %zu: "
+                        "run it once on this stream before capturing it", need, st->scratch_bytes);
         size_t want = need < (1u << 20) ? (1u << 20) : need + need / 4;
         want = (want + 255) & ~size_t(255);
-        if (st->scratch) B200_TRY(pool_free(d, st->scratch, st->s));
+        if (st->scratch && st->scratch_in_graph) st->retired.push_back(st->scratch);
+        else if (st->scratch) B200_TRY(pool_free(d, st->scratch, st->s));
+        st->scratch_in_graph = false;
         st->scratch = nullptr;
         st->scratch_bytes = 0;
         B200_TRY(pool_alloc(d, &st->scratch, want, st->s, "operator scratch"));
         st->scratch_bytes = want;
         B200_CUDA(cudaMemsetAsync(st->scratch, 0, kCounterBytes, st->s));
     }
+    if (capturing) st->scratch_in_graph = true;
     if (counters) *counters = reinterpret_cast<unsigned int*>(st->scratch);
     *out = reinterpret_cast<char*>(st->scratch) + kCounterBytes;
     return B200_OK;
@@ -327,7 +341,7 @@ int32_t b200_stream_create(int32_t dev, int32_t priority, b200_stream_t* out) {
     int p = priority < 0 ? hi : (priority > 0 ? lo : (lo + hi) / 2);
     cudaStream_t s;
     B200_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, p));
-    *out = new b200_stream_s{dev, s, true, nullptr, 0};
+    *out = new b200_stream_s{dev, s, true, nullptr, 0, false, {}};
     return B200_OK;
 }
 
@@ -335,7 +349,7 @@ int32_t b200_stream_wrap(int32_t dev, void* cuda_stream, b200_stream_t* out) {
     if (!out) return fail(B200_INVALID_ARG, "null output");
     DeviceState* d;
     B200_TRY(device_state(dev, &d));
-    *out = new b200_stream_s{dev, (cudaStream_t)cuda_stream, false, nullptr, 0};
+    *out = new b200_stream_s{dev, (cudaStream_t)cuda_stream, false, nullptr, 0, false, {}};
     return B200_OK;
 }
 
@@ -344,6 +358,7 @@ int32_t b200_stream_destroy(b200_stream_t st) {
     DeviceState* d;
     B200_TRY(device_state(st->dev, &d));
     if (st->scratch) pool_free(d, st->scratch, st->s);
+    for (void* p : st->retired) pool_free(d, p, st->s);
     if (st->owned) {
         cudaError_t e = cudaStreamDestroy(st->s);   // deferred by the runtime until work drains
         if (e != cudaSuccess) cudaGetLastError();
@@ -550,3 +565,98 @@ int32_t b200_host_unregister(void* ptr) {
 }
 
 }  // extern "C"
+
+
+// ---- graphs --------------------------------------------------------------------------------------------
+// Capture / instantiate / launch / update, the operations of src/hip/graph.jl:16-168.  Every
+// operator of this library can be captured: they only enqueue kernels and memsets on the stream
+// they are given.  The one host-side state an operator may change is the stream's scratch
+// buffer; it cannot grow inside a capture (see scratch()), so an operation is run once before it
+// is captured - what the reference's @captured does anyway when its first capture fails.
+struct b200_graph_s { int dev; cudaGraph_t g; };
+struct b200_graph_exec_s { int dev; cudaGraphExec_t e; };
+
+extern "C" int32_t b200_graph_capture_begin(b200_stream_t st, int32_t mode) {
+    B200_TRY(enter(st));
+    if (mode < 0 || mode > 2) return fail(B200_INVALID_ARG, "capture mode must be 0 (global), 1 (thread local) or 2 (relaxed)");
+    const cudaStreamCaptureMode m = mode == 0 ? cudaStreamCaptureModeGlobal
+                                   : mode == 1 ? cudaStreamCaptureModeThreadLocal : cudaStreamCaptureModeRelaxed;
+    B200_CUDA(cudaStreamBeginCapture(st->s, m));
+    return B200_OK;
+}
+
+extern "C" int32_t b200_graph_capture_end(b200_stream_t st, b200_graph_t* out) {
+    if (!out) return fail(B200_INVALID_ARG, "null output");
+    *out = nullptr;
+    B200_TRY(enter(st));
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(st->s, &g);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        if (g) cudaGraphDestroy(g);
+        return cuda_fail(e, "ending the stream capture (a call that cannot be captured invalidates it)");
+    }
+    *out = new b200_graph_s{st->dev, g};
+    return B200_OK;
+}
+
+extern "C" int32_t b200_stream_is_capturing(b200_stream_t st, int32_t* out) {
+    if (!out) return fail(B200_INVALID_ARG, "null output");
+    B200_TRY(enter(st));
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    B200_CUDA(cudaStreamIsCapturing(st->s, &cap));
+    *out = cap != cudaStreamCaptureStatusNone ? 1 : 0;
+    return B200_OK;
+}
+
+extern "C" int32_t b200_graph_destroy(b200_graph_t g) {
+    if (!g) return B200_OK;
+    DeviceState* d;
+    B200_TRY(device_state(g->dev, &d));
+    cudaError_t e = cudaGraphDestroy(g->g);
+    delete g;
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphDestroy");
+    return B200_OK;
+}
+
+extern "C" int32_t b200_graph_instantiate(b200_graph_t g, b200_graph_exec_t* out) {
+    if (!g || !out) return fail(B200_INVALID_ARG, "null graph or output");
+    DeviceState* d;
+    B200_TRY(device_state(g->dev, &d));
+    cudaGraphExec_t e = nullptr;
+    // allocations captured without their free are released when the graph is launched again
+    B200_CUDA(cudaGraphInstantiateWithFlags(&e, g->g, cudaGraphInstantiateFlagAutoFreeOnLaunch));
+    *out = new b200_graph_exec_s{g->dev, e};
+    return B200_OK;
+}
+
+extern "C" int32_t b200_graph_exec_destroy(b200_graph_exec_t e) {
+    if (!e) return B200_OK;
+    DeviceState* d;
+    B200_TRY(device_state(e->dev, &d));
+    cudaError_t err = cudaGraphExecDestroy(e->e);
+    delete e;
+    if (err != cudaSuccess) return cuda_fail(err, "cudaGraphExecDestroy");
+    return B200_OK;
+}
+
+extern "C" int32_t b200_graph_launch(b200_graph_exec_t e, b200_stream_t st) {
+    if (!e) return fail(B200_INVALID_ARG, "null executable graph");
+    B200_TRY(enter(st));
+    if (st->dev != e->dev) return fail(B200_INVALID_ARG, "graph of device %d launched on a stream of device %d", e->dev, st->dev);
+    B200_CUDA(cudaGraphLaunch(e->e, st->s));
+    return B200_OK;
+}
+
+extern "C" int32_t b200_graph_exec_update(b200_graph_exec_t e, b200_graph_t g, int32_t* updated) {
+    if (!e || !g || !updated) return fail(B200_INVALID_ARG, "null argument");
+    *updated = 0;
+    DeviceState* d;
+    B200_TRY(device_state(e->dev, &d));
+    cudaGraphExecUpdateResultInfo info{};
+    cudaError_t err = cudaGraphExecUpdate(e->e, g->g, &info);
+    if (err == cudaSuccess && info.result == cudaGraphExecUpdateSuccess) { *updated = 1; return B200_OK; }
+    cudaGetLastError();
+    if (err == cudaErrorGraphExecUpdateFailure || err == cudaSuccess) return B200_OK;   // topology differs: not an error, *updated stays 0
+    return cuda_fail(err, "cudaGraphExecUpdate");
+}

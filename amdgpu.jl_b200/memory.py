@@ -8,10 +8,13 @@ the collector of the host language stays outside the C code.
 """
 from __future__ import annotations
 
+import builtins
+import contextlib
 import ctypes as C
 import gc
 import math
 import os
+import threading
 
 from . import _lib
 from ._lib import OutOfMemoryError, check, lib
@@ -130,3 +133,130 @@ def used_memory(dev: int | None = None) -> int:
 def cached_memory(dev: int | None = None) -> int:
     s = pool_stats(dev)
     return s["pool_reserved"] - s["pool_used"]
+
+
+# ---- allocation cache (GPUArrays.AllocCache / @cached, hooked in src/array.jl:24-32) --------------------
+
+class AllocCache:
+    """Buffers allocated while the cache is active (``with cached(cache):``) belong to the cache:
+    the arrays' finalisers and ``unsafe_free_`` leave them alone, leaving the block marks them
+    free, and the next pass through the block gets the same buffers back for requests of the same
+    size on the same device.  Repeated iterations then make no allocator calls at all, which is
+    also what lets a block with temporaries be captured into a graph
+    (test/core/graph_tests.jl:37-55)."""
+
+    def __init__(self):
+        self._lock = threading.Lock()
+        self.free: dict[tuple[int, int], list[int]] = {}
+        self.busy: list[tuple[tuple[int, int], int]] = []
+
+    def take(self, key: tuple[int, int], alloc) -> int:
+        with self._lock:
+            pool = self.free.get(key)
+            ptr = pool.pop() if pool else None
+        if ptr is None:
+            ptr = alloc()
+        with self._lock:
+            self.busy.append((key, ptr))
+        return ptr
+
+    def release_busy(self) -> None:
+        with self._lock:
+            for key, ptr in self.busy:
+                self.free.setdefault(key, []).append(ptr)
+            self.busy.clear()
+
+    def sizeof(self) -> int:
+        with self._lock:
+            return builtins.sum(k[1] * len(v) for k, v in self.free.items()) + builtins.sum(k[1] for k, _ in self.busy)
+
+    def unsafe_free_(self, stream: Stream | None = None) -> None:
+        """``unsafe_free!(cache)``: hand every buffer back to the pool."""
+        with self._lock:
+            ptrs = [p for v in self.free.values() for p in v] + [p for _, p in self.busy]
+            self.free.clear()
+            self.busy.clear()
+        for p in ptrs:
+            pool_free(p, stream)
+
+
+class _CacheTLS(threading.local):
+    def __init__(self):
+        self.stack: list[AllocCache] = []
+
+
+_cache_tls = _CacheTLS()
+
+
+def current_cache() -> "AllocCache | None":
+    return _cache_tls.stack[-1] if _cache_tls.stack else None
+
+
+@contextlib.contextmanager
+def cached(cache: AllocCache):
+    """``GPUArrays.@cached cache expr``."""
+    _cache_tls.stack.append(cache)
+    try:
+        yield cache
+    finally:
+        _cache_tls.stack.pop()
+        cache.release_busy()
+
+
+# ---- idle pool trimming (pool_cleanup, src/memory.jl:289-321) ------------------------------------------
+
+class PoolCleanup:
+    """Every `interval` seconds look at each device's pool: if nothing was allocated from it for
+    `idle_periods` consecutive looks, return its cached memory to the driver (``reclaim``).
+    `activity(dev)` returns a monotonically growing allocation counter; `trim(dev)` does the
+    reclaim - both injectable so the policy can be tested without a device."""
+
+    def __init__(self, devices_fn, activity, trim, interval: float = 60.0, idle_periods: int = 5):
+        self.devices_fn, self.activity, self.trim = devices_fn, activity, trim
+        self.interval, self.idle_periods = interval, idle_periods
+        self._last: dict[int, int] = {}
+        self._idle: dict[int, int] = {}
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+
+    def step(self) -> list[int]:
+        """One look at all devices; returns the devices that were trimmed."""
+        trimmed = []
+        for dev in self.devices_fn():
+            count = self.activity(dev)
+            if count is None:
+                continue
+            if count != self._last.get(dev):
+                self._idle[dev] = 0
+            else:
+                self._idle[dev] = self._idle.get(dev, 0) + 1
+            self._last[dev] = count
+            if self._idle[dev] >= self.idle_periods:
+                self.trim(dev)
+                trimmed.append(dev)
+        return trimmed
+
+    def start(self) -> "PoolCleanup":
+        if self._thread is None:
+            def run():
+                while not self._stop.wait(self.interval):
+                    try:
+                        self.step()
+                    except Exception:
+                        pass
+            self._thread = threading.Thread(target=run, name="b200-pool-cleanup", daemon=True)
+            self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+            self._thread = None
+
+
+def start_pool_cleanup(interval: float = 60.0, idle_periods: int = 5) -> PoolCleanup:
+    """The reference starts this task with the package (src/memory.jl:289-321); here it is opt-in."""
+    from .runtime import devices
+    return PoolCleanup(devices, lambda d: pool_stats(d)["alloc_count"], lambda d: reclaim(d),
+                       interval, idle_periods).start()

@@ -81,6 +81,8 @@ typedef struct b200_stream_s* b200_stream_t;
 typedef struct b200_event_s*  b200_event_t;
 typedef struct b200_comm_s*   b200_comm_t;
 typedef struct b200_peer_s*   b200_peer_t;
+typedef struct b200_graph_s*      b200_graph_t;
+typedef struct b200_graph_exec_s* b200_graph_exec_t;
 
 /* Dense array view.  Mirrors what ROCArray hands to a kernel (src/array.jl:19-39: buffer, dims,
  * byte offset; pointer = base + offset, src/array.jl:353-354). */
@@ -253,6 +255,25 @@ int32_t b200_reverse(b200_stream_t st, const b200_tensor* y, const b200_tensor* 
  * 3: integers in [lo,hi], 4: raw low bits.  Counter based, so any slice can be regenerated. */
 int32_t b200_fill_random(b200_stream_t st, const b200_tensor* out, int32_t dist, uint64_t seed,
                          uint64_t stream_id, uint64_t first_index, int64_t lo, int64_t hi);
+
+/* ---- graphs (replaces src/hip/graph.jl:16-168: capture, instantiate, launch, update,
+ * is_capturing) --------------------------------------------------------------------------- */
+/* Every operator above can be captured.  An operator that needs more stream scratch than the
+ * stream holds answers B200_UNSUPPORTED inside a capture: run the operation once on that stream
+ * first (what @captured does when its first capture fails, src/hip/graph.jl:139-168).  Scratch seen
+ * by a capture stays allocated as long as the stream lives.  mode: 0 global, 1 thread local,
+ * 2 relaxed (hipStreamCaptureMode). */
+int32_t b200_graph_capture_begin(b200_stream_t st, int32_t mode);
+/* *out = NULL and an error status when the capture was invalidated */
+int32_t b200_graph_capture_end(b200_stream_t st, b200_graph_t* out);
+int32_t b200_stream_is_capturing(b200_stream_t st, int32_t* out);
+int32_t b200_graph_destroy(b200_graph_t g);
+/* allocations captured without their free are released at the next launch of the same graph */
+int32_t b200_graph_instantiate(b200_graph_t g, b200_graph_exec_t* out);
+int32_t b200_graph_exec_destroy(b200_graph_exec_t e);
+int32_t b200_graph_launch(b200_graph_exec_t e, b200_stream_t st);
+/* *updated = 1 when `e` now runs `g`; 0 (with B200_OK) when the topologies differ and `e` is unchanged */
+int32_t b200_graph_exec_update(b200_graph_exec_t e, b200_graph_t g, int32_t* updated);
 
 /* ---- multi-GPU (one process per GPU) ----------------------------------------------------- */
 /* The reference has no collective layer (multi-GPU is one task per device with host copies,

@@ -94,3 +94,63 @@ def test_view_geometry_matches_numpy(pkg):
         A.subview(6, slice(None), slice(None))
     with pytest.raises(ValueError):
         A.permuteddims((1, 1, 2))
+
+
+def test_alloc_cache_reuses_buffers(pkg, monkeypatch):
+    """GPUArrays.@cached semantics with the allocator faked: the second pass through a cached
+    block makes no allocator call, frees inside the block are no-ops, unsafe_free_ returns all."""
+    import sys
+    arr = sys.modules[pkg.ROCArray.__module__]
+    mem = sys.modules[pkg.AllocCache.__module__]
+    calls = {"alloc": 0, "free": []}
+
+    def fake_alloc(nbytes, stream=None):
+        calls["alloc"] += 1
+        return 0x1000 * calls["alloc"]
+
+    monkeypatch.setattr(arr, "pool_alloc", fake_alloc)
+    monkeypatch.setattr(arr, "pool_free", lambda ptr, stream=None: calls["free"].append(ptr))
+    monkeypatch.setattr(mem, "pool_free", lambda ptr, stream=None: calls["free"].append(ptr))
+
+    class FakeStream:
+        device, handle = 0, 1
+
+    def block():
+        a = pkg.ROCArray(np.float32, (4, 4), stream=FakeStream())
+        b = pkg.ROCArray(np.float32, (4, 4), stream=FakeStream())
+        c = pkg.ROCArray(np.int64, 3, stream=FakeStream())
+        ptrs = (a.ptr, b.ptr, c.ptr)
+        a.unsafe_free_()                      # no-op: the cache owns it
+        return ptrs
+
+    cache = pkg.AllocCache()
+    with pkg.cached(cache):
+        first = block()
+    assert calls["alloc"] == 3 and calls["free"] == []
+    assert cache.sizeof() == 64 + 64 + 24
+    with pkg.cached(cache):
+        second = block()
+    assert calls["alloc"] == 3                # everything came back from the cache
+    assert sorted(second) == sorted(first)
+    outside = pkg.ROCArray(np.float32, (4, 4), stream=FakeStream())      # not cached
+    assert calls["alloc"] == 4
+    outside.unsafe_free_()
+    assert calls["free"] == [outside.buf.ptr]
+    cache.unsafe_free_()
+    assert sorted(calls["free"][1:]) == sorted(first) and cache.sizeof() == 0
+
+
+def test_pool_cleanup_policy(pkg):
+    """pool_cleanup (src/memory.jl:289-321): trim a device's pool after five idle looks in a row."""
+    counts = {0: 10, 1: 5}
+    trimmed = []
+    pc = pkg.PoolCleanup(lambda: [0, 1], lambda d: counts[d], trimmed.append, interval=3600, idle_periods=5)
+    assert pc.step() == []                    # first look only records the counters
+    for i in range(4):
+        counts[1] += 1                        # device 1 stays busy
+        assert pc.step() == []
+    assert pc.step() == [0] and trimmed == [0]
+    counts[0] += 1                            # activity resets the idle count
+    assert pc.step() == []
+    assert pc.step() == [] and pc.step() == []
+    assert pc.step() == [1] and trimmed == [0, 1]     # device 1 has now been idle five looks in a row
