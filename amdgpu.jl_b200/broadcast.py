@@ -210,6 +210,27 @@ def materialize_(dest: ROCArray, bc, stream: Stream | None = None) -> ROCArray:
     return dest
 
 
+def precompile(dest: ROCArray, bc) -> bool:
+    """Compiles the kernel specialised for ``dest .= bc`` without launching anything (the library
+    otherwise does it on the first call with a new expression structure, as the reference's JIT
+    does).  False when the run-time compiler is unavailable: the expression is then interpreted."""
+    bc = Broadcasted.leaf(bc)
+    code, leaves, nleaves, _keep = bc.flatten()
+    t = dest.tensor()
+    return lib.b200_broadcast_prepare(C.byref(t), leaves, nleaves, code, len(code) // 2) == 0
+
+
+def jit_configure(enable: bool) -> None:
+    """Switches run-time specialisation of broadcast expressions on or off (default on)."""
+    check(lib.b200_jit_configure(1 if enable else 0))
+
+
+def jit_stats() -> dict:
+    out = (C.c_uint64 * 4)()
+    check(lib.b200_jit_stats(out))
+    return {"compiled": out[0], "hits": out[1], "failures": out[2], "enabled": bool(out[3])}
+
+
 def prepared(dest: ROCArray, bc, stream: Stream | None = None):
     """Flattens ``dest .= bc`` once and returns a zero-argument callable that re-issues the same
     launch; for call sites that repeat one expression and want the host cost of a bare C call."""

@@ -46,13 +46,35 @@ def _stamp(src: Path) -> str:
     return h.hexdigest()
 
 
+def _write_rtc_sources() -> None:
+    """The run-time compiler (csrc/jit.cu) builds its kernels from the evaluator's own sources:
+    they are embedded in the library as string literals through this generated include file."""
+    def lit(name: str, path: Path) -> str:
+        text = path.read_text()
+        # one literal per ~8 KB: compilers limit the length of a single string literal
+        chunks = [text[i:i + 8000] for i in range(0, len(text), 8000)] or [""]
+        body = "\n".join(f'R"b200src({c})b200src"' for c in chunks)
+        return f"static const char {name}[] =\n{body};\n"
+    out = OBJ / "rtc_sources.inc"
+    # of the public header only the types and constants: host prototypes mean nothing to NVRTC
+    header = (HERE.parent / "include" / "b200arrays.h").read_text()
+    marker = "/* ---- library / device"
+    assert marker in header, "b200arrays.h lost the marker that separates types from entry points"
+    types_only = OBJ / "b200arrays_types.h"
+    types_only.write_text(header[:header.index(marker)] + "#ifdef __cplusplus\n}\n#endif\n#endif\n")
+    text = (lit("kRtcCommon", CSRC / "common.cuh") + lit("kRtcProgram", CSRC / "program.cuh")
+            + lit("kRtcHeader", types_only))
+    if not out.exists() or out.read_text() != text:
+        out.write_text(text)
+
+
 def _compile_one(src: Path, verbose: bool) -> Path:
     obj = OBJ / (src.stem + ".o")
     stamp = OBJ / (src.stem + ".stamp")
     want = _stamp(src)
     if obj.exists() and stamp.exists() and stamp.read_text() == want:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(OBJ), "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -70,6 +92,7 @@ def build_library(verbose: bool = False, force: bool = False) -> Path:
     if force:
         for f in OBJ.glob("*.stamp"):
             f.unlink()
+    _write_rtc_sources()
     srcs = sorted(CSRC.glob("*.cu"))
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(lambda s: _compile_one(s, verbose), srcs))

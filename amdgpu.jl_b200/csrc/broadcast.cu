@@ -273,32 +273,6 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
     return B200_OK;
 }
 
-// ---- device: evaluator kernel -------------------------------------------------------------------------
-template <bool WIDE>
-__global__ void __launch_bounds__(256, WIDE ? 2 : 3)
-ew_program_kernel(const __grid_constant__ ProgramDesc P, const __grid_constant__ LeafDesc O, int64_t n) {
-    using R = typename RawOf<WIDE>::type;
-    const int64_t nvec = (n + kVec - 1) / kVec;
-    const bool out_linear = P.linear != 0;
-    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
-        int64_t lin[kVec];
-#pragma unroll
-        for (int j = 0; j < kVec; ++j) lin[j] = v * kVec + j;
-        const int64_t left = n - v * kVec;
-        const int nvalid = left < kVec ? (int)left : kVec;
-        R res[kVec];
-        eval_program<WIDE>(P, lin, nvalid, res);
-        if (out_linear) {
-            store_vec4<R>(const_cast<void*>(O.ptr), O.dtype, lin[0], P.vec_ok != 0, nvalid, res);
-        } else {
-            const int bytes = dtype_bytes(O.dtype);
-#pragma unroll
-            for (int j = 0; j < kVec; ++j)
-                if (j < nvalid) store_bits(const_cast<void*>(O.ptr), bytes, leaf_offset(P, O, lin[j]), encode<R>(O.dtype, res[j]));
-        }
-    }
-}
-
 // ---- device: hard-wired streaming kernels --------------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<float> {
@@ -560,6 +534,25 @@ static bool try_fixed(b200_stream_t st, const Compiled& C, const std::vector<Nod
 
 using namespace b200;
 
+// Destination descriptor and the layout flags that depend on it.
+static void destination_layout(const b200_tensor* out, Compiled* C, LeafDesc* O) {
+    O->ptr = out->ptr;
+    O->dtype = out->dtype;
+    for (int d = 0; d < out->ndim; ++d) O->stride[d] = out->shape[d] == 1 ? 0 : out->stride[d];
+    if (!tensor_is_contiguous(out)) C->P.linear = 0;
+    if (!C->P.linear || reinterpret_cast<uintptr_t>(out->ptr) % (dtype_size(out->dtype) * kVec) != 0) C->P.vec_ok = 0;
+}
+
+extern "C" int32_t b200_broadcast_prepare(const b200_tensor* out, const b200_leaf* leaves, int32_t nleaves,
+                                          const uint8_t* program, int32_t ninstr) {
+    B200_TRY(check_tensor(out, "broadcast destination"));
+    Compiled C;
+    B200_TRY(compile_program(out->shape, out->ndim, leaves, nleaves, program, ninstr, out->dtype, &C));
+    LeafDesc O{};
+    destination_layout(out, &C, &O);
+    return jit_prepare(C, out->dtype);
+}
+
 extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, const b200_leaf* leaves,
                                   int32_t nleaves, const uint8_t* program, int32_t ninstr) {
     B200_TRY(enter(st));
@@ -572,12 +565,7 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
         if (out->shape[d] > 1 && out->stride[d] == 0) return fail(B200_INVALID_ARG, "broadcast destination has a zero stride");
 
     LeafDesc O{};
-    O.ptr = out->ptr;
-    O.dtype = out->dtype;
-    for (int d = 0; d < out->ndim; ++d) O.stride[d] = out->shape[d] == 1 ? 0 : out->stride[d];
-    const bool out_dense = tensor_is_contiguous(out);
-    if (!out_dense) C.P.linear = 0;
-    if (!C.P.linear || reinterpret_cast<uintptr_t>(out->ptr) % (dtype_size(out->dtype) * kVec) != 0) C.P.vec_ok = 0;
+    destination_layout(out, &C, &O);
 
     // Hard-wired kernels: every array leaf dense, same dtype as the destination, no conversions.
     if (C.P.linear) {
@@ -603,6 +591,9 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
         }
     }
 
+    // any other tree: the evaluator specialised for this expression at run time if possible,
+    // else the interpreter
+    if (jit_broadcast(st, C, O, n)) return finish(st, "b200_broadcast");
     const int64_t nvec = (n + kVec - 1) / kVec;
     const int64_t chunks = (nvec + 255) / 256;
     if (C.wide) ew_program_kernel<true><<<balanced_grid(chunks, resident_blocks(ew_program_kernel<true>, 256, 0, st->dev)), 256, 0, st->s>>>(C.P, O, n);

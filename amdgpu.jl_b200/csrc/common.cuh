@@ -1,16 +1,23 @@
 // Internal declarations shared by the translation units of libb200arrays.so.
 #pragma once
 
+// Under run-time compilation (NVRTC, which defines __CUDACC_RTC__) only the device-side half of
+// this header is seen: the specialised broadcast kernels are built from the very same sources.
+#ifndef __CUDACC_RTC__
 #include <cuda_runtime.h>
+#endif
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stddef.h>
+#ifndef __CUDACC_RTC__
 #include <string>
 #include <vector>
+#endif
 
 #include "../../include/b200arrays.h"
 
+#ifndef __CUDACC_RTC__
 // ---- host-side handles ---------------------------------------------------------------------
 struct b200_stream_s {
     int          dev;
@@ -130,6 +137,7 @@ int32_t check_tensor(const b200_tensor* t, const char* name);
 int32_t peer_next_context(b200_peer_t peer, b200_stream_t st, PeerCtx* out);
 
 }  // namespace b200
+#endif  // !__CUDACC_RTC__
 
 // ---- device-side helpers --------------------------------------------------------------------
 #ifdef __CUDACC__

@@ -71,15 +71,22 @@ struct Compiled {
     int32_t n_array_leaves;
 };
 
+#ifndef __CUDACC_RTC__
 // Validates `program` against `leaves` and the index space `shape`; appends a conversion to
 // `final_dtype` when that is >= 0 and differs from the program's result type.
 int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
                         int32_t nleaves, const uint8_t* program, int32_t ninstr,
                         int32_t final_dtype, Compiled* out);
 
+// Run-time specialisation (jit.cu): launch the kernel compiled for exactly this expression, if
+// there is one (false: the caller runs the interpreter); compile it without launching.
+bool jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n);
+int32_t jit_prepare(const Compiled& C, int out_dtype);
+
 // Converts one scalar between its storage bits and the class representation (host side).
 uint64_t scalar_to_class(int32_t dtype, uint64_t bits);
 uint64_t class_to_storage(int32_t dtype, uint64_t cls);
+#endif  // !__CUDACC_RTC__
 
 #ifdef __CUDACC__
 
@@ -436,35 +443,53 @@ __device__ __forceinline__ int64_t leaf_offset(const ProgramDesc& P, const LeafD
     return off;
 }
 
-template <typename R>
+// Where the evaluator takes its instruction stream from.  DynamicCode: the program travels in the
+// kernel parameter and every instruction is decoded at run time (the interpreter).  A run-time
+// compiled kernel instead supplies a type with the same members as compile-time constants
+// (is_static = true); the loops below then unroll, every switch folds and what is left is
+// straight-line code for that one expression - same helpers, same roundings, same results.
+struct DynamicCode {
+    static constexpr bool is_static = false;
+    static constexpr int ninstr = 0, nleaves = 0, linear = 0, vec_ok = 0, out_dtype = 0;
+    static constexpr unsigned char hcode[2] = {0, 0};
+    static constexpr unsigned char leaf_dtype[1] = {0};
+    static constexpr unsigned char leaf_scalar[1] = {0};
+};
+
+template <typename R, typename S = DynamicCode>
 __device__ __forceinline__ void fetch_leaf(const ProgramDesc& P, int k, const int64_t lin[kVec], int nvalid, R out[kVec]) {
     const LeafDesc& L = P.leaves[k];
-    if (L.is_scalar) {
+    const int dt = S::is_static ? (int)S::leaf_dtype[S::is_static ? k : 0] : L.dtype;
+    const bool scalar = S::is_static ? S::leaf_scalar[S::is_static ? k : 0] != 0 : L.is_scalar != 0;
+    const bool linear = S::is_static ? S::linear != 0 : P.linear != 0;
+    const bool vec_ok = S::is_static ? S::vec_ok != 0 : P.vec_ok != 0;
+    if (scalar) {
 #pragma unroll
         for (int j = 0; j < kVec; ++j) out[j] = (R)L.scalar;
         return;
     }
-    if (P.linear) {
-        load_vec4<R>(L.ptr, L.dtype, lin[0], P.vec_ok != 0, nvalid, out);
+    if (linear) {
+        load_vec4<R>(L.ptr, dt, lin[0], vec_ok, nvalid, out);
     } else {
-        const int bytes = dtype_bytes(L.dtype);
+        const int bytes = dtype_bytes(dt);
 #pragma unroll
         for (int j = 0; j < kVec; ++j)
-            out[j] = (j < nvalid) ? decode<R>(L.dtype, load_bits(L.ptr, bytes, leaf_offset(P, L, lin[j]))) : (R)0;
+            out[j] = (j < nvalid) ? decode<R>(dt, load_bits(L.ptr, bytes, leaf_offset(P, L, lin[j]))) : (R)0;
     }
 }
 
 // Evaluates the program for the index-space elements lin[0..nvalid).  In linear mode lin[] must
 // be consecutive and lin[0] a multiple of kVec.
-template <bool WIDE>
+template <bool WIDE, typename S = DynamicCode>
 __device__ __forceinline__ void eval_program(const ProgramDesc& P, const int64_t lin[kVec], int nvalid,
                                              typename RawOf<WIDE>::type result[kVec]) {
     using R = typename RawOf<WIDE>::type;
+    const int nleaves = S::is_static ? S::nleaves : P.nleaves;
     // Issue the loads of the first array leaves before decoding anything, so that they overlap.
     R pre[kPrefetch][kVec];
 #pragma unroll
     for (int k = 0; k < kPrefetch; ++k) {
-        if (k < P.nleaves) fetch_leaf<R>(P, k, lin, nvalid, pre[k]);
+        if (k < nleaves) fetch_leaf<R, S>(P, k, lin, nvalid, pre[k]);
     }
     // s0 is the top of the stack; a push moves every slot one down, a pop one up
     R s0[kVec], s1[kVec], s2[kVec], s3[kVec], s4[kVec];
@@ -488,32 +513,40 @@ __device__ __forceinline__ void eval_program(const ProgramDesc& P, const int64_t
     case kHOps + CID * kNumOps + 8: B200_BIN(C, Arith<C>::max(x, y))                      \
     case kHOps + CID * kNumOps + 9: B200_BIN(C, Arith<C>::min(x, y))                      \
     case kHOps + CID * kNumOps + 10: B200_UN(C, Arith<C>::neg(x))
-    for (int pc = 0; pc < P.ninstr; ++pc) {
-        const int h = P.hcode[2 * pc], arg = P.hcode[2 * pc + 1];
-        switch (h) {
-            case kHPre0: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[0][j]; break;
-            case kHPre1: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[1][j]; break;
-            case kHPre2: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[2][j]; break;
-            case kHPre3: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[3][j]; break;
-            case kHLeafMem: B200_SHIFT_DOWN() fetch_leaf<R>(P, arg, lin, nvalid, s0); break;
-            case kHConvert: exec_convert<WIDE, R>(arg, s0); break;
-            B200_CLASS_CASES(CF32, float)
-            B200_CLASS_CASES(CI32, int32_t)
-            B200_CLASS_CASES(CU32, uint32_t)
-            default:
-                if constexpr (WIDE) {
-                    switch (h) {
-                        B200_CLASS_CASES(CF64, double)
-                        B200_CLASS_CASES(CI64, int64_t)
-                        B200_CLASS_CASES(CU64, uint64_t)
-                        default: break;
-                    }
-                }
-                break;
-        }
-        // operators on narrow element types re-round / re-wrap their result (operand = that dtype)
+#define B200_EVAL_STEP \
+        const int h = S::is_static ? (int)S::hcode[S::is_static ? 2 * pc : 0] : (int)P.hcode[2 * pc]; \
+        const int arg = S::is_static ? (int)S::hcode[S::is_static ? 2 * pc + 1 : 1] : (int)P.hcode[2 * pc + 1]; \
+        switch (h) { \
+            case kHPre0: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[0][j]; break; \
+            case kHPre1: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[1][j]; break; \
+            case kHPre2: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[2][j]; break; \
+            case kHPre3: B200_SHIFT_DOWN() _Pragma("unroll") for (int j = 0; j < kVec; ++j) s0[j] = pre[3][j]; break; \
+            case kHLeafMem: B200_SHIFT_DOWN() fetch_leaf<R, S>(P, arg, lin, nvalid, s0); break; \
+            case kHConvert: exec_convert<WIDE, R>(arg, s0); break; \
+            B200_CLASS_CASES(CF32, float) \
+            B200_CLASS_CASES(CI32, int32_t) \
+            B200_CLASS_CASES(CU32, uint32_t) \
+            default: \
+                if constexpr (WIDE) { \
+                    switch (h) { \
+                        B200_CLASS_CASES(CF64, double) \
+                        B200_CLASS_CASES(CI64, int64_t) \
+                        B200_CLASS_CASES(CU64, uint64_t) \
+                        default: break; \
+                    } \
+                } \
+                break; \
+        } \
+        /* operators on narrow element types re-round / re-wrap their result (operand = that dtype) */ \
         if (h >= kHOps && arg != 0xff) narrow_vec<R>(arg, s0);
+    if constexpr (S::is_static) {
+#pragma unroll
+        for (int pc = 0; pc < S::ninstr; ++pc) { B200_EVAL_STEP }
+    } else {
+#pragma unroll 1
+        for (int pc = 0; pc < P.ninstr; ++pc) { B200_EVAL_STEP }
     }
+#undef B200_EVAL_STEP
 #undef B200_CLASS_CASES
 #undef B200_TER
 #undef B200_BIN
@@ -523,6 +556,41 @@ __device__ __forceinline__ void eval_program(const ProgramDesc& P, const int64_t
 #undef B200_SHIFT_DOWN
 #pragma unroll
     for (int j = 0; j < kVec; ++j) result[j] = s0[j];
+}
+
+// The broadcast loop over an arbitrary program: one vector of kVec elements per thread and step.
+// Instantiated with DynamicCode inside the library (ew_program_kernel, the interpreter) and with
+// a constant program by the run-time compiler (jit.cu wraps it in an extern "C" kernel).
+template <bool WIDE, typename S = DynamicCode>
+__device__ __forceinline__ void ew_program_body(const ProgramDesc& P, const LeafDesc& O, int64_t n) {
+    using R = typename RawOf<WIDE>::type;
+    const int64_t nvec = (n + kVec - 1) / kVec;
+    const bool out_linear = S::is_static ? S::linear != 0 : P.linear != 0;
+    const bool vec_ok = S::is_static ? S::vec_ok != 0 : P.vec_ok != 0;
+    const int out_dtype = S::is_static ? (int)S::out_dtype : O.dtype;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+        int64_t lin[kVec];
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) lin[j] = v * kVec + j;
+        const int64_t left = n - v * kVec;
+        const int nvalid = left < kVec ? (int)left : kVec;
+        R res[kVec];
+        eval_program<WIDE, S>(P, lin, nvalid, res);
+        if (out_linear) {
+            store_vec4<R>(const_cast<void*>(O.ptr), out_dtype, lin[0], vec_ok, nvalid, res);
+        } else {
+            const int bytes = dtype_bytes(out_dtype);
+#pragma unroll
+            for (int j = 0; j < kVec; ++j)
+                if (j < nvalid) store_bits(const_cast<void*>(O.ptr), bytes, leaf_offset(P, O, lin[j]), encode<R>(out_dtype, res[j]));
+        }
+    }
+}
+
+template <bool WIDE>
+__global__ void __launch_bounds__(256, WIDE ? 2 : 3)
+ew_program_kernel(const __grid_constant__ ProgramDesc P, const __grid_constant__ LeafDesc O, int64_t n) {
+    ew_program_body<WIDE, DynamicCode>(P, O, n);
 }
 
 #endif  // __CUDACC__

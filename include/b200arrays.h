@@ -194,6 +194,20 @@ int32_t b200_host_unregister(void* ptr);
  * (style selection: src/broadcast.jl:3-30): out[I] = program(leaves[I]...) */
 int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, const b200_leaf* leaves,
                        int32_t nleaves, const uint8_t* program, int32_t ninstr);
+/* Broadcast expressions outside the hard-wired set run through an evaluator that the library
+ * specialises for the expression at run time (the counterpart of the reference compiling each
+ * broadcast kernel with GPUCompiler on first use, src/broadcast.jl:3-35 + GPUArrays): the first
+ * call with a new expression STRUCTURE (operators, element types, dense/strided) compiles for a
+ * few hundred milliseconds, later calls reuse the kernel whatever the pointers, sizes and scalar
+ * values.  b200_broadcast_prepare compiles without launching (no device needed; the check_tensor
+ * rules of b200_broadcast apply, data is not touched); B200_UNSUPPORTED when the run-time compiler
+ * (libnvrtc) is not available - b200_broadcast then interprets the expression on the GPU instead.
+ * b200_jit_configure(0) switches specialisation off (env B200_JIT=0 does the same);
+ * b200_jit_stats: out[0] kernels compiled, out[1] cache hits, out[2] failures, out[3] enabled. */
+int32_t b200_broadcast_prepare(const b200_tensor* out, const b200_leaf* leaves, int32_t nleaves,
+                               const uint8_t* program, int32_t ninstr);
+int32_t b200_jit_configure(int32_t enable);
+int32_t b200_jit_stats(uint64_t out[4]);
 
 /* replaces GPUArrays.mapreducedim!(f, op, R, A; init) (src/kernels/mapreduce.jl:86-173).
  * The map f (possibly a whole broadcast tree) is given as a program over `leaves`; the index
