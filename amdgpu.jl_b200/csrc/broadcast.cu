@@ -593,7 +593,11 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
 
     // any other tree: the evaluator specialised for this expression at run time if possible,
     // else the interpreter
-    if (jit_broadcast(st, C, O, n)) return finish(st, "b200_broadcast");
+    const int specialised = jit_broadcast(st, C, O, n);
+    if (specialised > 0) return finish(st, "b200_broadcast");
+    if (specialised < 0)
+        return fail(B200_UNSUPPORTED, "first use of this broadcast expression inside a stream capture: its kernel has to "
+                    "be compiled and loaded, run the expression once before capturing");
     const int64_t nvec = (n + kVec - 1) / kVec;
     const int64_t chunks = (nvec + 255) / 256;
     if (C.wide) ew_program_kernel<true><<<balanced_grid(chunks, resident_blocks(ew_program_kernel<true>, 256, 0, st->dev)), 256, 0, st->s>>>(C.P, O, n);

@@ -195,15 +195,24 @@ int32_t jit_prepare(const Compiled& C, int out_dtype) {
     return B200_OK;
 }
 
-// Launches the specialised kernel for this expression if there is one.  False: caller interprets.
-bool jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n) {
+// Launches the specialised kernel for this expression if there is one.  1: launched; 0: there is
+// none, the caller interprets; -1: the kernel would have to be compiled or loaded now and the
+// stream is being captured - the caller reports that the expression must run once outside a
+// capture first (loading code is not something a capture can record).
+int jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n) {
     cudaKernel_t kernel = nullptr;
     int per_sm = 0;
     {
         std::lock_guard<std::mutex> lk(g_mu);
-        if (!enabled()) return false;
+        if (!enabled()) return 0;
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st->s, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
+        if (cap != cudaStreamCaptureStatusNone) {
+            auto it = g_cache.find(cache_key(C, O.dtype));
+            if (it == g_cache.end() || (!it->second.cubin.empty() && !it->second.kernel)) return -1;
+        }
         Entry* e = lookup(C, O.dtype);
-        if (!e) return false;
+        if (!e) return 0;
         if (!e->kernel) {
             if (cudaLibraryLoadData(&e->lib, e->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0) != cudaSuccess ||
                 cudaLibraryGetKernel(&e->kernel, e->lib, "b200_jit_kernel") != cudaSuccess) {
@@ -211,7 +220,7 @@ bool jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64
                 ++g_failures;
                 e->cubin.clear();
                 e->kernel = nullptr;
-                return false;
+                return 0;
             }
             int b = 0;
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, (const void*)e->kernel, 256, 0) != cudaSuccess || b < 1) {
@@ -229,9 +238,9 @@ bool jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64
     void* args[] = {(void*)&C.P, (void*)&O, (void*)&nn};
     if (cudaLaunchKernel((const void*)kernel, dim3(grid), dim3(256), args, 0, st->s) != cudaSuccess) {
         cudaGetLastError();
-        return false;
+        return 0;
     }
-    return true;
+    return 1;
 }
 
 }  // namespace b200

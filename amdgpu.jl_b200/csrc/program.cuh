@@ -78,9 +78,10 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
                         int32_t nleaves, const uint8_t* program, int32_t ninstr,
                         int32_t final_dtype, Compiled* out);
 
-// Run-time specialisation (jit.cu): launch the kernel compiled for exactly this expression, if
-// there is one (false: the caller runs the interpreter); compile it without launching.
-bool jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n);
+// Run-time specialisation (jit.cu): launch the kernel compiled for exactly this expression
+// (1), report that there is none so that the caller interprets (0), or that it cannot be built
+// inside a stream capture (-1); compile it without launching.
+int jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n);
 int32_t jit_prepare(const Compiled& C, int out_dtype);
 
 // Converts one scalar between its storage bits and the class representation (host side).

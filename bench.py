@@ -196,20 +196,26 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
         if want("c1_cumsum"):
             rec("c1_cumsum_2p24_f32", 8 * n, time_loop(pkg, st, rotate([pkg.accumulate_prepared("+", z, x) for x, _, z in sets]), reps(200)))
         del sets
-    # the same kind of expression through the generic evaluator (a tree the hard-wired kernels do
-    # not match): how fast an arbitrary fused broadcast runs
+    # expressions the hard-wired kernels do not match: how fast an arbitrary fused broadcast runs,
+    # with the evaluator specialised for the expression at run time (the default) and interpreted
     if want("gen"):
         n = (1 << 26) >> shrink
         xs = [R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM11, seed=4, stream_id=k) for k in range(3)]
         out_ = pkg.ROCArray(np.float32, n)
         bcm = pkg.broadcast
-        tree = xs[0].dot * xs[1].dot + bcm.exp(-bcm.abs_(xs[2])) + np.float32(0.25)
-        rec("gen_evaluator_x*y+exp(-abs(z))+c_2p26_f32", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(out_, tree), reps(20)))
-        tree2 = bcm.maximum(xs[0].dot - xs[1].dot, xs[2].dot * np.float32(2))
-        rec("gen_evaluator_max(x-y,2z)_2p26_f32", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(out_, tree2), reps(20)))
         xi = R.fill_random_(pkg.ROCArray(np.int32, n), R.INTEGERS, seed=2, lo=-100, hi=100)
         outd = pkg.ROCArray(np.float64, n)
-        rec("gen_evaluator_i32*f32->f64_2p26", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(outd, xi.dot * xs[0].dot * 1.5), reps(20)))
+        trees = (("x*y+exp(-abs(z))+c_2p26_f32", out_, lambda: xs[0].dot * xs[1].dot + bcm.exp(-bcm.abs_(xs[2])) + np.float32(0.25)),
+                 ("max(x-y,2z)_2p26_f32", out_, lambda: bcm.maximum(xs[0].dot - xs[1].dot, xs[2].dot * np.float32(2))),
+                 ("i32*f32->f64_2p26", outd, lambda: xi.dot * xs[0].dot * 1.5))
+        for mode, on in (("specialised", True), ("interpreted", False)):
+            bcm.jit_configure(on)
+            try:
+                for name, dest, tree in trees:
+                    rec(f"gen_{mode}_{name}", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(dest, tree()), reps(20)))
+            finally:
+                bcm.jit_configure(True)
+        out["gen_runtime_compiler"] = bcm.jit_stats()
         del xs, out_, xi, outd
     # config 2: 8192 x 8192 matrices
     if want("c2"):

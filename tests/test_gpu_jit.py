@@ -48,7 +48,10 @@ def test_specialised_kernels_match_the_interpreter(gpu):
     after = B.jit_stats()
     if after["failures"] > before["failures"] and after["compiled"] == before["compiled"]:
         pytest.skip("no run-time compiler on this machine: the interpreter ran both times")
-    assert after["compiled"] >= before["compiled"] + 6 and after["hits"] > before["hits"]
+    # 36 evaluations went through the specialised path: each either compiled a kernel or found one
+    # (other tests of the same process may have compiled some of these structures already)
+    assert after["compiled"] + after["hits"] >= before["compiled"] + before["hits"] + 36
+    assert after["hits"] > before["hits"]
 
 
 def test_specialised_kernels_on_strided_and_broadcast_operands(gpu):
