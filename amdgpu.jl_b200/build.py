@@ -63,7 +63,7 @@ def _write_rtc_sources() -> None:
     types_only = OBJ / "b200arrays_types.h"
     types_only.write_text(header[:header.index(marker)] + "#ifdef __cplusplus\n}\n#endif\n#endif\n")
     text = (lit("kRtcCommon", CSRC / "common.cuh") + lit("kRtcProgram", CSRC / "program.cuh")
-            + lit("kRtcHeader", types_only))
+            + lit("kRtcReduce", CSRC / "reduce_program.cuh") + lit("kRtcHeader", types_only))
     if not out.exists() or out.read_text() != text:
         out.write_text(text)
 

@@ -11,7 +11,7 @@
 // expression's structure (operators, element types, layout flags; pointers, shapes and scalar
 // values stay run-time arguments).  NVRTC is loaded with dlopen; when it is missing, or a
 // compilation fails, the interpreter runs instead - still on the GPU.
-#include "program.cuh"
+#include "reduce_program.cuh"
 
 #include <dlfcn.h>
 #include <nvrtc.h>
@@ -23,7 +23,7 @@
 #include <string>
 #include <vector>
 
-#include "rtc_sources.inc"   // kRtcCommon, kRtcProgram, kRtcHeader: the sources above as strings
+#include "rtc_sources.inc"   // kRtcCommon, kRtcProgram, kRtcReduce, kRtcHeader: the sources as strings
 
 namespace b200 {
 
@@ -89,8 +89,12 @@ bool enabled() {
 }
 
 // Everything the generated code depends on, and nothing else.
-std::string cache_key(const Compiled& C, int out_dtype) {
+struct ReduceInfo { int redop, acc_dtype, full; };
+
+std::string cache_key(const Compiled& C, int out_dtype, const ReduceInfo* red = nullptr) {
     std::string k;
+    if (red) { k.push_back('R'); k.push_back((char)red->redop); k.push_back((char)red->acc_dtype); k.push_back((char)red->full); }
+    else k.push_back('B');
     k.push_back(C.wide ? 'W' : 'N');
     k.push_back((char)C.P.ninstr);
     k.append(reinterpret_cast<const char*>(C.P.hcode), 2 * (size_t)C.P.ninstr);
@@ -114,17 +118,30 @@ std::string byte_list(const unsigned char* p, int n) {
     return n ? s : std::string("0");
 }
 
-std::string generate_source(const Compiled& C, int out_dtype) {
+std::string generate_source(const Compiled& C, int out_dtype, const ReduceInfo* red = nullptr) {
     const ProgramDesc& P = C.P;
     unsigned char ld[B200_MAX_LEAVES + 1] = {0}, ls[B200_MAX_LEAVES + 1] = {0};
     for (int i = 0; i < P.nleaves; ++i) { ld[i] = (unsigned char)P.leaves[i].dtype; ls[i] = P.leaves[i].is_scalar ? 1 : 0; }
-    std::string s = "#include \"program.cuh\"\nnamespace b200 {\nstruct StaticCode {\n    static constexpr bool is_static = true;\n";
+    std::string s = red ? "#include \"reduce_program.cuh\"\n" : "#include \"program.cuh\"\n";
+    s += "namespace b200 {\nstruct StaticCode {\n    static constexpr bool is_static = true;\n";
+    s += "    static constexpr int redop = " + std::to_string(red ? red->redop : 0) + ", acc_dtype = " +
+         std::to_string(red ? red->acc_dtype : 0) + ", full = " + std::to_string(red ? red->full : 0) + ";\n";
     s += "    static constexpr int ninstr = " + std::to_string(P.ninstr) + ", nleaves = " + std::to_string(P.nleaves) +
          ", linear = " + std::to_string(P.linear ? 1 : 0) + ", vec_ok = " + std::to_string(P.vec_ok ? 1 : 0) +
          ", out_dtype = " + std::to_string(out_dtype) + ";\n";
     s += "    static constexpr unsigned char hcode[] = {" + byte_list(P.hcode, 2 * P.ninstr) + "};\n";
     s += "    static constexpr unsigned char leaf_dtype[] = {" + byte_list(ld, P.nleaves) + "};\n";
     s += "    static constexpr unsigned char leaf_scalar[] = {" + byte_list(ls, P.nleaves) + "};\n};\n}\n";
+    if (red) {
+        s += "extern \"C\" __global__ void __launch_bounds__(256) b200_jit_reduce_kernel(const __grid_constant__ b200::ProgramDesc P, "
+             "const __grid_constant__ b200::LeafDesc O, const __grid_constant__ b200::GenericPlan G, void* partials, "
+             "unsigned int* counters, b200::RedOut out) {\n    b200::reduce_program_body<";
+        s += C.wide ? "true" : "false";
+        s += ", b200::StaticCode>(P, O, G, (b200::RawOf<";
+        s += C.wide ? "true" : "false";
+        s += ">::type*)partials, counters, out);\n}\n";
+        return s;
+    }
     s += "extern \"C\" __global__ void __launch_bounds__(256, 3) b200_jit_kernel(const __grid_constant__ b200::ProgramDesc P, "
          "const __grid_constant__ b200::LeafDesc O, long long n) {\n    b200::ew_program_body<";
     s += C.wide ? "true" : "false";
@@ -143,10 +160,10 @@ const char kStddef[] = "#pragma once\ntypedef unsigned long size_t;\n";
 
 bool compile(const std::string& src, std::vector<char>* cubin) {
     if (!load_nvrtc()) { g_last_log = "libnvrtc could not be loaded"; return false; }
-    const char* header_src[] = {kRtcProgram, kRtcCommon, kRtcHeader, kStdint, kStddef};
-    const char* header_names[] = {"program.cuh", "common.cuh", "../../include/b200arrays.h", "stdint.h", "stddef.h"};
+    const char* header_src[] = {kRtcProgram, kRtcCommon, kRtcReduce, kRtcHeader, kStdint, kStddef};
+    const char* header_names[] = {"program.cuh", "common.cuh", "reduce_program.cuh", "../../include/b200arrays.h", "stdint.h", "stddef.h"};
     nvrtcProgram prog = nullptr;
-    if (g_nvrtc.CreateProgram(&prog, src.c_str(), "b200_jit.cu", 5, header_src, header_names) != NVRTC_SUCCESS) return false;
+    if (g_nvrtc.CreateProgram(&prog, src.c_str(), "b200_jit.cu", 6, header_src, header_names) != NVRTC_SUCCESS) return false;
     std::string inc = std::string("-I") + (getenv("B200_CUDA_INCLUDE") ? getenv("B200_CUDA_INCLUDE") : "/usr/local/cuda/include");
     const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", inc.c_str()};
     const nvrtcResult r = g_nvrtc.CompileProgram(prog, 4, opts);
@@ -170,8 +187,8 @@ bool compile(const std::string& src, std::vector<char>* cubin) {
 }
 
 // Looks the expression up, compiling it on a miss.  Returns null when no specialised kernel exists.
-Entry* lookup(const Compiled& C, int out_dtype) {
-    const std::string key = cache_key(C, out_dtype);
+Entry* lookup(const Compiled& C, int out_dtype, const ReduceInfo* red = nullptr) {
+    const std::string key = cache_key(C, out_dtype, red);
     auto it = g_cache.find(key);
     if (it != g_cache.end()) {
         if (it->second.cubin.empty()) return nullptr;
@@ -179,7 +196,7 @@ Entry* lookup(const Compiled& C, int out_dtype) {
         return &it->second;
     }
     Entry e;
-    if (compile(generate_source(C, out_dtype), &e.cubin)) ++g_compiled;
+    if (compile(generate_source(C, out_dtype, red), &e.cubin)) ++g_compiled;
     else { ++g_failures; e.cubin.clear(); }
     Entry& slot = g_cache[key] = std::move(e);
     return slot.cubin.empty() ? nullptr : &slot;
@@ -199,39 +216,44 @@ int32_t jit_prepare(const Compiled& C, int out_dtype) {
 // none, the caller interprets; -1: the kernel would have to be compiled or loaded now and the
 // stream is being captured - the caller reports that the expression must run once outside a
 // capture first (loading code is not something a capture can record).
+static int acquire(b200_stream_t st, const Compiled& C, int out_dtype, const ReduceInfo* red, const char* symbol,
+                   cudaKernel_t* kernel, int* per_sm) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!enabled()) return 0;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st->s, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
+    if (cap != cudaStreamCaptureStatusNone) {
+        auto it = g_cache.find(cache_key(C, out_dtype, red));
+        if (it == g_cache.end() || (!it->second.cubin.empty() && !it->second.kernel)) return -1;
+    }
+    Entry* e = lookup(C, out_dtype, red);
+    if (!e) return 0;
+    if (!e->kernel) {
+        if (cudaLibraryLoadData(&e->lib, e->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0) != cudaSuccess ||
+            cudaLibraryGetKernel(&e->kernel, e->lib, symbol) != cudaSuccess) {
+            cudaGetLastError();
+            ++g_failures;
+            e->cubin.clear();
+            e->kernel = nullptr;
+            return 0;
+        }
+        int b = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, (const void*)e->kernel, 256, 0) != cudaSuccess || b < 1) {
+            cudaGetLastError();
+            b = 3;
+        }
+        e->blocks_per_sm = b;
+    }
+    *kernel = e->kernel;
+    *per_sm = e->blocks_per_sm;
+    return 1;
+}
+
 int jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n) {
     cudaKernel_t kernel = nullptr;
     int per_sm = 0;
-    {
-        std::lock_guard<std::mutex> lk(g_mu);
-        if (!enabled()) return 0;
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(st->s, &cap) != cudaSuccess) { cudaGetLastError(); cap = cudaStreamCaptureStatusNone; }
-        if (cap != cudaStreamCaptureStatusNone) {
-            auto it = g_cache.find(cache_key(C, O.dtype));
-            if (it == g_cache.end() || (!it->second.cubin.empty() && !it->second.kernel)) return -1;
-        }
-        Entry* e = lookup(C, O.dtype);
-        if (!e) return 0;
-        if (!e->kernel) {
-            if (cudaLibraryLoadData(&e->lib, e->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0) != cudaSuccess ||
-                cudaLibraryGetKernel(&e->kernel, e->lib, "b200_jit_kernel") != cudaSuccess) {
-                cudaGetLastError();
-                ++g_failures;
-                e->cubin.clear();
-                e->kernel = nullptr;
-                return 0;
-            }
-            int b = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, (const void*)e->kernel, 256, 0) != cudaSuccess || b < 1) {
-                cudaGetLastError();
-                b = 3;
-            }
-            e->blocks_per_sm = b;
-        }
-        kernel = e->kernel;
-        per_sm = e->blocks_per_sm;
-    }
+    const int got = acquire(st, C, O.dtype, nullptr, "b200_jit_kernel", &kernel, &per_sm);
+    if (got <= 0) return got;
     const int64_t nvec = (n + kVec - 1) / kVec;
     const unsigned grid = balanced_grid((nvec + 255) / 256, (int64_t)per_sm * sm_count(st->dev));
     long long nn = n;
@@ -240,6 +262,21 @@ int jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_
         cudaGetLastError();
         return 0;
     }
+    return 1;
+}
+
+// The specialised kernel for mapreducedim! over this map expression: same return values as
+// jit_broadcast; on 1, *kernel takes (ProgramDesc, LeafDesc, GenericPlan, partials, counters,
+// RedOut) like reduce_program_kernel and *resident is one wave of its blocks on this device.
+int jit_reduce_kernel(b200_stream_t st, const Compiled& C, int out_dtype, int redop, int acc_dtype, int full,
+                      const void** kernel, int64_t* resident) {
+    const ReduceInfo red{redop, acc_dtype, full};
+    cudaKernel_t k = nullptr;
+    int per_sm = 0;
+    const int got = acquire(st, C, out_dtype, &red, "b200_jit_reduce_kernel", &k, &per_sm);
+    if (got <= 0) return got;
+    *kernel = (const void*)k;
+    *resident = (int64_t)per_sm * sm_count(st->dev);
     return 1;
 }
 

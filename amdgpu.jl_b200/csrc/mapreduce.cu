@@ -15,7 +15,7 @@
 // tree as the mapped function, several operands, gaps in the reduced dimensions, strided
 // views - goes through the program evaluator.  Algorithmic traffic: sizeof(T) per input
 // element plus the outputs.
-#include "program.cuh"
+#include "reduce_program.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -25,7 +25,6 @@
 namespace b200 {
 
 enum { MAP_ID = 0, MAP_ABS = 1, MAP_ABS2 = 2 };
-constexpr int kRedThreads = 256;
 
 // ---- operator algebra ---------------------------------------------------------------------------------
 template <typename Acc, int OP>
@@ -133,12 +132,6 @@ __device__ __forceinline__ Acc fold_lanes(const Acc acc[V]) {
     return r;
 }
 
-struct RedOut {
-    void*    R;
-    int32_t  rdtype;
-    int32_t  use_init;
-    uint64_t init;      // class bits of the accumulator type
-};
 
 template <typename Acc, int OP>
 __device__ __forceinline__ void finalize(const RedOut& o, int64_t idx, Acc v) {
@@ -446,131 +439,6 @@ reduce_strided_kernel(const Tin* A, StridedPlan pl, int mapop, Acc* partials, un
 #undef CALL
 }
 
-// ---- evaluator path -------------------------------------------------------------------------------------
-struct GenericPlan {
-    int64_t n_out, n_red;
-    int     B;             // blocks per output
-    int64_t chunk;         // reduced elements per block
-    uint32_t reduced_mask; // bit d set: dimension d is reduced
-    int32_t full;          // every dimension reduced: index = r, linear access allowed
-    int32_t redop, acc_dtype;
-    uint64_t identity;     // class bits
-};
-
-template <typename C, typename R>
-__device__ __forceinline__ R red_raw_c(int redop, R a, R b) {
-    using A = Arith<C>;
-    const C x = as_c<C>(a), y = as_c<C>(b);
-    switch (redop) {
-        case B200_RED_ADD: return raw_of<R>(A::add(x, y));
-        case B200_RED_MUL: return raw_of<R>(A::mul(x, y));
-        case B200_RED_MAX: return raw_of<R>(A::max(x, y));
-        default: return raw_of<R>(A::min(x, y));
-    }
-}
-template <bool WIDE, typename R>
-__device__ __forceinline__ R red_raw(int redop, int cls, R a, R b) {
-    switch (cls) {
-        case CF32: return red_raw_c<float>(redop, a, b);
-        case CI32: return red_raw_c<int32_t>(redop, a, b);
-        case CU32: return red_raw_c<uint32_t>(redop, a, b);
-        default:
-            if constexpr (WIDE) {
-                if (cls == CF64) return red_raw_c<double>(redop, a, b);
-                if (cls == CI64) return red_raw_c<int64_t>(redop, a, b);
-                return red_raw_c<uint64_t>(redop, a, b);
-            }
-            return a;
-    }
-}
-
-template <bool WIDE>
-__global__ void __launch_bounds__(kRedThreads)
-reduce_program_kernel(const __grid_constant__ ProgramDesc P, const __grid_constant__ LeafDesc O,
-                      const __grid_constant__ GenericPlan G, typename RawOf<WIDE>::type* partials,
-                      unsigned int* counters, RedOut out) {
-    using R = typename RawOf<WIDE>::type;
-    __shared__ R smem[kRedThreads];
-    __shared__ int s_last;
-    const int cls = dtype_class(G.acc_dtype);
-    const int64_t items = G.n_out * G.B;
-    for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
-        const int64_t o = item / G.B;
-        const int b = (int)(item - o * G.B);
-        const int64_t rbeg = (int64_t)b * G.chunk;
-        int64_t rend = rbeg + G.chunk;
-        if (rend > G.n_red) rend = G.n_red;
-        R acc = (R)G.identity;
-        for (int64_t r = rbeg + (int64_t)threadIdx.x * kVec; r < rend; r += (int64_t)blockDim.x * kVec) {
-            const int64_t left = rend - r;
-            const int nvalid = left < kVec ? (int)left : kVec;
-            int64_t lin[kVec];
-            if (G.full) {
-#pragma unroll
-                for (int j = 0; j < kVec; ++j) lin[j] = r + j;
-            } else {
-#pragma unroll
-                for (int j = 0; j < kVec; ++j) {
-                    int64_t rr = r + j, oo = o, mult = 1, li = 0;
-                    for (int d = 0; d < P.ndim; ++d) {
-                        const int64_t e = P.shape[d];
-                        int64_t idx;
-                        if ((G.reduced_mask >> d) & 1u) { idx = rr % e; rr /= e; }
-                        else { idx = oo % e; oo /= e; }
-                        li += idx * mult;
-                        mult *= e;
-                    }
-                    lin[j] = li;
-                }
-            }
-            R res[kVec];
-            eval_program<WIDE>(P, lin, nvalid, res);
-#pragma unroll
-            for (int j = 0; j < kVec; ++j) if (j < nvalid) acc = red_raw<WIDE, R>(G.redop, cls, acc, res[j]);
-        }
-        smem[threadIdx.x] = acc;
-        __syncthreads();
-        for (int s = kRedThreads / 2; s > 0; s >>= 1) {
-            if ((int)threadIdx.x < s) smem[threadIdx.x] = red_raw<WIDE, R>(G.redop, cls, smem[threadIdx.x], smem[threadIdx.x + s]);
-            __syncthreads();
-        }
-        R v = smem[0];
-        __syncthreads();
-        bool write = (G.B == 1);
-        if (G.B > 1) {
-            if (threadIdx.x == 0) {
-                partials[o * G.B + b] = v;
-                __threadfence();
-                const unsigned int t = atomicAdd(&counters[o], 1u);
-                s_last = (t == (unsigned int)(G.B - 1));
-                if (s_last) counters[o] = 0;
-            }
-            __syncthreads();
-            if (s_last && threadIdx.x == 0) {
-                __threadfence();
-                v = (R)G.identity;
-                for (int j = 0; j < G.B; ++j) v = red_raw<WIDE, R>(G.redop, cls, v, __ldcg(&partials[o * G.B + j]));
-                write = true;
-            }
-            __syncthreads();
-        }
-        if (write && threadIdx.x == 0) {
-            // offset of output o inside R (reduced dimensions have extent 1 there)
-            int64_t oo = o, off = 0;
-            for (int d = 0; d < P.ndim; ++d) {
-                if ((G.reduced_mask >> d) & 1u) continue;
-                const int64_t e = P.shape[d];
-                off += (oo % e) * O.stride[d];
-                oo /= e;
-            }
-            const int bytes = dtype_bytes(O.dtype);
-            R seed = out.use_init ? (R)out.init : decode<R>(O.dtype, load_bits(O.ptr, bytes, off));
-            v = red_raw<WIDE, R>(G.redop, cls, seed, v);
-            store_bits(const_cast<void*>(O.ptr), bytes, off, encode<R>(O.dtype, v));
-        }
-    }
-}
-
 // ---- host ------------------------------------------------------------------------------------------------
 static int acc_dtype_of(int rdtype) {
     switch (dtype_class(rdtype)) {
@@ -778,7 +646,19 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
     G.acc_dtype = acc_dt;
     G.identity = identity_bits(op, acc_dt);
     if (!G.full) { C.P.linear = 0; C.P.vec_ok = 0; }
-    const int64_t target = C.wide ? resident_blocks(reduce_program_kernel<true>, kRedThreads, 0, st->dev)
+    // the kernel specialised for this expression at run time if there is one, else the interpreter
+    LeafDesc O{};
+    O.ptr = R->ptr;
+    O.dtype = R->dtype;
+    for (int d = 0; d < ndim; ++d) O.stride[d] = (d < R->ndim && R->shape[d] != 1) ? R->stride[d] : 0;
+    const void* special = nullptr;
+    int64_t special_resident = 0;
+    const int got = jit_reduce_kernel(st, C, O.dtype, op, acc_dt, G.full, &special, &special_resident);
+    if (got < 0)
+        return fail(B200_UNSUPPORTED, "first use of this mapreduce expression inside a stream capture: its kernel has to "
+                    "be compiled and loaded, run the expression once before capturing");
+    const int64_t target = special ? special_resident
+                         : C.wide ? resident_blocks(reduce_program_kernel<true>, kRedThreads, 0, st->dev)
                                   : resident_blocks(reduce_program_kernel<false>, kRedThreads, 0, st->dev);
     int64_t B = target / n_out;
     const int64_t min_chunk = 16384;
@@ -794,11 +674,13 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
     void* scr = nullptr;
     unsigned int* counters = nullptr;
     B200_TRY(scratch(st, (size_t)(n_out * B) * 8, &scr, &counters));
-    LeafDesc O{};
-    O.ptr = R->ptr;
-    O.dtype = R->dtype;
-    for (int d = 0; d < ndim; ++d) O.stride[d] = (d < R->ndim && R->shape[d] != 1) ? R->stride[d] : 0;
     const unsigned blocks = balanced_grid(n_out * B, target);
+    if (special) {
+        void* args[] = {(void*)&C.P, (void*)&O, (void*)&G, (void*)&scr, (void*)&counters, (void*)&out};
+        if (cudaLaunchKernel(special, dim3(blocks), dim3(kRedThreads), args, 0, st->s) == cudaSuccess)
+            return finish(st, "b200_mapreduce");
+        cudaGetLastError();      // fall through to the interpreter
+    }
     if (C.wide) reduce_program_kernel<true><<<blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint64_t*)scr, counters, out);
     else reduce_program_kernel<false><<<blocks, kRedThreads, 0, st->s>>>(C.P, O, G, (uint32_t*)scr, counters, out);
     return finish(st, "b200_mapreduce");

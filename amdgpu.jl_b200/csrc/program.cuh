@@ -83,6 +83,8 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
 // inside a stream capture (-1); compile it without launching.
 int jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n);
 int32_t jit_prepare(const Compiled& C, int out_dtype);
+int jit_reduce_kernel(b200_stream_t st, const Compiled& C, int out_dtype, int redop, int acc_dtype, int full,
+                      const void** kernel, int64_t* resident);
 
 // Converts one scalar between its storage bits and the class representation (host side).
 uint64_t scalar_to_class(int32_t dtype, uint64_t bits);
@@ -452,6 +454,7 @@ __device__ __forceinline__ int64_t leaf_offset(const ProgramDesc& P, const LeafD
 struct DynamicCode {
     static constexpr bool is_static = false;
     static constexpr int ninstr = 0, nleaves = 0, linear = 0, vec_ok = 0, out_dtype = 0;
+    static constexpr int redop = 0, acc_dtype = 0, full = 0;      // reductions only (reduce_program.cuh)
     static constexpr unsigned char hcode[2] = {0, 0};
     static constexpr unsigned char leaf_dtype[1] = {0};
     static constexpr unsigned char leaf_scalar[1] = {0};

@@ -215,6 +215,15 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
                     rec(f"gen_{mode}_{name}", 16 * n, time_loop(pkg, st, pkg.broadcast.prepared(dest, tree()), reps(20)))
             finally:
                 bcm.jit_configure(True)
+        # a reduction over a two-operand map expression (dot product): 8 B per element
+        r1 = pkg.ROCArray(np.float32, 1)
+        for mode, on in (("specialised", True), ("interpreted", False)):
+            bcm.jit_configure(on)
+            try:
+                rec(f"gen_{mode}_sum(x.*y)_2p26_f32", 8 * n,
+                    time_loop(pkg, st, pkg.mapreduce_prepared(None, "+", r1, xs[0].dot * xs[1].dot, init=np.float32(0)), reps(20)))
+            finally:
+                bcm.jit_configure(True)
         out["gen_runtime_compiler"] = bcm.jit_stats()
         del xs, out_, xi, outd
     # config 2: 8192 x 8192 matrices

@@ -76,3 +76,38 @@ def test_specialised_kernels_on_strided_and_broadcast_operands(gpu):
     if s1["compiled"] > s0["compiled"]:
         assert s1["compiled"] == s0["compiled"] + 1 and s1["hits"] >= s0["hits"] + 2
     assert B.precompile(gpu.ROCArray(np.float32, 10), x.dot * np.float32(5) + B.abs_(x.dot) * B.abs_(x.dot)) in (True, False)
+
+
+def test_specialised_reductions_match_the_interpreter(gpu):
+    """mapreduce over a map expression with several operands (dot products, distances ...)."""
+    B = gpu.broadcast
+    rng = np.random.default_rng(23)
+    H, K = rng.standard_normal((300, 41, 7)).astype(np.float32), rng.standard_normal((300, 41, 7)).astype(np.float32)
+    Hd, Kd = gpu.ROCArray.from_host(np.asfortranarray(H)), gpu.ROCArray.from_host(np.asfortranarray(K))
+    ints = gpu.ROCArray.from_host(rng.integers(-9, 9, 100_003).astype(np.int32))
+    half = gpu.ROCArray.from_host(rng.standard_normal(100_003).astype(np.float16))
+    cases = [
+        (lambda: gpu.mapreduce(None, "+", Hd.dot * Kd.dot), None),                         # dot product
+        (lambda: gpu.mapreduce(None, "+", B.abs2(Hd.dot - Kd.dot), dims=1), None),
+        (lambda: gpu.mapreduce(None, "max", B.abs_(Hd.dot - Kd.dot), dims=(1, 3)), None),
+        (lambda: gpu.mapreduce(None, "min", Hd.dot * np.float32(2) + Kd.dot, dims=2), None),
+        (lambda: gpu.mapreduce(None, "+", ints.dot * ints.dot - 3), None),
+        (lambda: gpu.mapreduce(None, "+", half.dot * half.dot + ints.dot), None),
+    ]
+    before = B.jit_stats()
+    for build, _ in cases:
+        outs = []
+        for jit in (True, False):
+            B.jit_configure(jit)
+            try:
+                r = build()
+                outs.append(r.to_host() if hasattr(r, "to_host") else np.asarray(r))
+            finally:
+                B.jit_configure(True)
+        assert bits_equal(outs[0], outs[1])
+    ref = (H.astype(np.float64) * K).sum()
+    assert abs(float(gpu.mapreduce(None, "+", Hd.dot * Kd.dot)) - ref) <= 1e-5 * abs(ref) + 1e-3
+    after = B.jit_stats()
+    if after["compiled"] == before["compiled"] and after["failures"] > before["failures"]:
+        pytest.skip("no run-time compiler on this machine")
+    assert after["compiled"] + after["hits"] >= before["compiled"] + before["hits"] + 6
