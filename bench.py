@@ -320,7 +320,7 @@ def main():
     rank, world, local_rank = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")))
     warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     n = 1 << args.log2_elems
-    workload = (f"config5 shard: r .= x.*y .+ exp.(-abs.(z)); sum(abs2, r) + NCCL allreduce; 2^{args.log2_elems} Float32 "
+    workload = (f"config5 shard: r .= x.*y .+ exp.(-abs.(z)); sum(abs2, r) all-reduced over the ranks (--collective fused: inside the reduction kernel over NVLink peer memory; nccl: separate NCCL call); 2^{args.log2_elems} Float32 "
                 f"elements per GPU (2^33 total at 8 GPUs)")
 
     if args.impl == "reference":
