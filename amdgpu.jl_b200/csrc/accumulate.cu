@@ -632,6 +632,196 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
     if (s_abort && tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
 }
 
+// ---- scan along a strided dimension (K > 1) -----------------------------------------------------------
+// cumsum(A; dims=2) and friends: neighbouring memory holds neighbouring COLUMNS, the scan runs
+// down the rows with stride K.  A block takes a tile of 32*VEC columns x 64 rows: a warp reads
+// row segments of 512 bytes (coalesced), every thread scans its VEC columns down the 8 rows of its
+// warp with 8 independent loads in flight, the 8 warps are stitched through shared memory, and
+// tiles below each other are chained with the same aggregate / inclusive-prefix protocol as the
+// 1-D scans - here the published value is a vector (one entry per column of the strip).  Tickets
+// hand tiles out row-band by row-band, so the tile above a tile was handed out a whole band
+// earlier and its prefix is normally waiting; HBM sees one read and one write per element.
+constexpr int kSsWarps = 8;
+constexpr int kSsRows = 8;                          // rows per warp
+constexpr int kSsLY = kSsWarps * kSsRows;           // rows per tile
+
+struct StridedScanPlan {
+    int64_t K, L, M;
+    int64_t S, NT;            // strips across K, tiles along L
+    int64_t ntiles;           // M * S * NT
+    int32_t inclusive, has_init;
+    uint32_t max_polls;
+    uint64_t init;
+    const void* init_dev;
+};
+
+template <typename T, int OP, int VEC>
+__global__ void __launch_bounds__(256)
+scan_strided_kernel(const T* A, T* B, StridedScanPlan pl, uint32_t* flags, typename ScanAcc<T>::type* agg,
+                    typename ScanAcc<T>::type* pre, unsigned int* ticket, int32_t* err_word) {
+    using Acc = typename ScanAcc<T>::type;
+    using VT = Vec<T, VEC>;
+    constexpr int KX = 32 * VEC;                    // columns per strip
+    __shared__ Acc s_tot[kSsWarps][KX];
+    __shared__ Acc s_pref[KX];
+    __shared__ long long s_tile;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        const unsigned int t = atomicAdd(ticket, 1u);
+        if ((int64_t)t == pl.ntiles - 1) *ticket = 0;   // nobody takes a ticket after the last tile
+        s_tile = t;
+        s_abort = 0;
+    }
+    __syncthreads();
+    // tickets walk strips and slabs fastest, row bands slowest
+    const int64_t id = s_tile;
+    const int64_t per_band = pl.M * pl.S;
+    const int64_t tt = id / per_band;
+    const int64_t rem = id - tt * per_band;
+    const int64_t m = rem / pl.S, s = rem - m * pl.S;
+    const int64_t d = (m * pl.S + s) * pl.NT + tt;      // descriptor index; the tile above is d - 1
+    const int64_t k0 = s * KX + lane * VEC;
+    const int64_t slab = m * pl.K * pl.L;
+    const int64_t l0 = tt * kSsLY + warp * kSsRows;
+
+    // ---- load 8 rows, scan down them
+    Acc x[kSsRows][VEC];
+#pragma unroll
+    for (int r = 0; r < kSsRows; ++r) {
+        const int64_t l = l0 + r;
+        const bool row_ok = l < pl.L;
+        if (VEC > 1) {
+            VT v;
+            const bool ok = row_ok && k0 < pl.K;
+            if (ok) v = *reinterpret_cast<const VT*>(A + slab + k0 + pl.K * l);
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) x[r][q] = ok ? scan_up<T>(v.v[q]) : scan_identity<Acc, OP>();
+        } else {
+            x[r][0] = (row_ok && k0 < pl.K) ? scan_up<T>(A[slab + k0 + pl.K * l]) : scan_identity<Acc, OP>();
+        }
+    }
+#pragma unroll
+    for (int r = 1; r < kSsRows; ++r)
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) x[r][q] = scan_apply<Acc, OP>(x[r - 1][q], x[r][q]);
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) s_tot[warp][lane * VEC + q] = x[kSsRows - 1][q];
+    __syncthreads();
+
+    // ---- one thread per column of the strip: aggregate, look-back, prefix
+    Acc column_total = scan_identity<Acc, OP>();
+    if (tid < KX) {
+        column_total = s_tot[0][tid];
+#pragma unroll
+        for (int w = 1; w < kSsWarps; ++w) column_total = scan_apply<Acc, OP>(column_total, s_tot[w][tid]);
+        if (tt == 0) {
+            Acc seed = scan_identity<Acc, OP>();
+            if (pl.has_init) seed = (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
+            s_pref[tid] = seed;
+            *reinterpret_cast<volatile Acc*>(pre + d * KX + tid) = pl.has_init ? scan_apply<Acc, OP>(seed, column_total) : column_total;
+        } else {
+            *reinterpret_cast<volatile Acc*>(agg + d * KX + tid) = column_total;
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    if (tid == 0) *reinterpret_cast<volatile uint32_t*>(flags + d) = (tt == 0) ? FLAG_PREFIX : FLAG_AGGREGATE;
+    if (tid < KX && tt > 0) {
+        Acc running = scan_identity<Acc, OP>();
+        bool set = false, failed = false;
+        for (int64_t p = d - 1;; --p) {                 // ends at the strip's first tile at the latest (always a full prefix)
+            uint32_t f = *reinterpret_cast<volatile uint32_t*>(flags + p);
+            uint32_t polls = 0;
+            while (f == FLAG_EMPTY) {
+                ++polls;
+                if (polls > pl.max_polls || ((polls & 1023u) == 0 && error_latched(err_word))) { failed = true; break; }
+                if (polls > 32) __nanosleep(polls > 4096 ? 256 : 32);
+                f = *reinterpret_cast<volatile uint32_t*>(flags + p);
+            }
+            if (failed) break;
+            __threadfence();
+            const Acc v = *reinterpret_cast<volatile Acc*>((f == FLAG_PREFIX ? pre : agg) + p * KX + tid);
+            running = set ? scan_apply<Acc, OP>(v, running) : v;
+            set = true;
+            if (f == FLAG_PREFIX) break;
+        }
+        if (failed) {
+            s_abort = 1;
+        } else {
+            s_pref[tid] = running;
+            *reinterpret_cast<volatile Acc*>(pre + d * KX + tid) = scan_apply<Acc, OP>(running, column_total);
+            __threadfence();
+        }
+    }
+    __syncthreads();
+    if (s_abort) {
+        if (tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
+        return;
+    }
+    if (tid == 0 && tt > 0) *reinterpret_cast<volatile uint32_t*>(flags + d) = FLAG_PREFIX;
+
+    // ---- offsets and stores
+    const bool seeded = tt > 0 || pl.has_init;
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) {
+        const int col = lane * VEC + q;
+        Acc o = scan_identity<Acc, OP>();
+        for (int w = 0; w < warp; ++w) o = scan_apply<Acc, OP>(o, s_tot[w][col]);
+        if (seeded) o = scan_apply<Acc, OP>(s_pref[col], o);
+        // x[r] becomes the output of row r (exclusive: the value of the row above)
+        Acc above = o;
+#pragma unroll
+        for (int r = 0; r < kSsRows; ++r) {
+            const Acc incl = scan_apply<Acc, OP>(o, x[r][q]);
+            x[r][q] = pl.inclusive ? incl : above;
+            above = incl;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kSsRows; ++r) {
+        const int64_t l = l0 + r;
+        if (l >= pl.L || k0 >= pl.K) continue;
+        if (VEC > 1) {
+            VT v;
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) v.v[q] = scan_down<T>(x[r][q]);
+            *reinterpret_cast<VT*>(B + slab + k0 + pl.K * l) = v;
+        } else {
+            B[slab + k0 + pl.K * l] = scan_down<T>(x[r][0]);
+        }
+    }
+}
+
+template <typename T, int OP, int VEC>
+static int32_t launch_scan_strided(b200_stream_t st, const void* A, void* B, const ScanPlan& pl) {
+    using Acc = typename ScanAcc<T>::type;
+    constexpr int KX = 32 * VEC;
+    StridedScanPlan sp{};
+    sp.K = pl.K; sp.L = pl.L; sp.M = pl.M;
+    sp.S = (pl.K + KX - 1) / KX;
+    sp.NT = (pl.L + kSsLY - 1) / kSsLY;
+    sp.ntiles = sp.M * sp.S * sp.NT;
+    if (sp.ntiles >= ((int64_t)1 << 31)) return fail(B200_TOO_LARGE, "accumulate: too many tiles");
+    sp.inclusive = pl.inclusive;
+    sp.has_init = pl.has_init;
+    sp.max_polls = pl.max_polls;
+    sp.init = pl.init;
+    sp.init_dev = pl.init_dev;
+    const size_t fbytes = ((size_t)sp.ntiles * sizeof(uint32_t) + 255) / 256 * 256;
+    const size_t vbytes = (size_t)sp.ntiles * KX * sizeof(Acc);
+    void* scr = nullptr;
+    unsigned int* counters = nullptr;
+    B200_TRY(scratch(st, fbytes + 2 * vbytes, &scr, &counters));
+    B200_CUDA(cudaMemsetAsync(scr, 0, fbytes, st->s));      // the flags; the value vectors need no clearing
+    unsigned char* base = reinterpret_cast<unsigned char*>(scr);
+    unsigned int* ticket = counters + (kCounterBytes / sizeof(unsigned int) - 1);
+    scan_strided_kernel<T, OP, VEC><<<(unsigned)sp.ntiles, 256, 0, st->s>>>(
+        (const T*)A, (T*)B, sp, reinterpret_cast<uint32_t*>(base), reinterpret_cast<Acc*>(base + fbytes),
+        reinterpret_cast<Acc*>(base + fbytes + vbytes), ticket, device_error_word(st->dev));
+    return B200_OK;
+}
+
 // One thread per column: sequential walk, coalesced across neighbouring columns when K > 1.
 template <typename T, int OP>
 __global__ void __launch_bounds__(256)
@@ -661,6 +851,12 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
     constexpr int TILE = kScanThreads * kScanVecs * V;
     const int64_t ncols = pl.K * pl.M;
     const int64_t target = (int64_t)sm_count(st->dev) * 8;
+    const bool aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0 && reinterpret_cast<uintptr_t>(B) % 16 == 0;
+    if (pl.K >= 32 && pl.L > 32) {      // long scans down a strided dimension: tiled, chained along L
+        constexpr int V = 16 / sizeof(T);
+        if (aligned && (pl.K * sizeof(T)) % 16 == 0) return launch_scan_strided<T, OP, V>(st, A, B, pl);
+        return launch_scan_strided<T, OP, 1>(st, A, B, pl);
+    }
     const bool thread_cols = (pl.L <= 32 && ncols >= 1024) || (pl.K > 1 && ncols >= 4096);
     if (thread_cols) {
         int64_t blocks = (ncols + 255) / 256;
@@ -668,7 +864,6 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         scan_column_thread_kernel<T, OP><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
         return B200_OK;
     }
-    const bool aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0 && reinterpret_cast<uintptr_t>(B) % 16 == 0;
     if (ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {
         SegPlan sp{};
         sp.nvec = pl.L * (int64_t)sizeof(T) / 16;

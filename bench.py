@@ -244,6 +244,15 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
             if want(f"c2_sumsq_8192_{tag}"):
                 rec(f"c2_sumsq_8192_{tag}", nb, time_loop(pkg, st, rotate([pkg.mapreduce_prepared("abs2", "+", r0, A, init=zero) for A in mats]), reps(50)))
             del mats
+    # scans along one dimension of a matrix (the shapes of the reference's own accumulate benchmarks,
+    # perf/array.jl:70-85, at B200 size): 8 B per element
+    if want("mat_cumsum"):
+        m = 8192 >> (shrink // 2)
+        A = R.fill_random_(pkg.ROCArray(np.float32, (m, m)), R.UNIFORM01, seed=2)
+        Bm = pkg.ROCArray(np.float32, (m, m))
+        for d in (1, 2):
+            rec(f"mat_cumsum_dims{d}_8192_f32", 8 * m * m, time_loop(pkg, st, pkg.accumulate_prepared("+", Bm, A, dims=d), reps(10)))
+        del A, Bm
     # config 3: 2^28 scans
     if want("c3") or want("c4_sort"):
         n = (1 << 28) >> shrink

@@ -112,3 +112,45 @@ def test_ring_kernel_small_types_and_variants(gpu, orc):
     assert L.lib.b200_accumulate_carry(gpu.current_stream().handle, C.byref(tb), C.byref(ta), L.RED_ADD,
                                        C.c_void_p(carry.ptr), 0, 1) == L.OK
     assert np.array_equal(out.to_host(), orc.accumulate("+", x, init=np.int32(1000)))
+
+
+@pytest.mark.parametrize("sizes", [(33, 500), (64, 300, 5), (128, 65), (1000, 130), (36, 64, 2), (257, 129)])
+def test_scans_down_a_strided_dimension(gpu, orc, sizes):
+    """accumulate(op, A; dims=2) with at least a warp of columns: the tiled kernel (vector and
+    scalar column access, several slabs, ragged edges), all operators, seeds, exclusive form."""
+    rng = np.random.default_rng(5)
+    for dt in (np.float32, np.float64, np.int32, np.float16):
+        dt = np.dtype(dt)
+        if dt.kind == "i":
+            x = rng.integers(-3, 4, sizes).astype(dt)
+        else:
+            x = (rng.random(sizes) + 0.5).astype(dt)
+        xd = gpu.ROCArray.from_host(x)
+        for op in ("+", "max", "min") + (("*",) if dt.kind == "f" and dt.itemsize >= 4 else ()):
+            xs = x if op != "*" else (0.9 + 0.2 * rng.random(sizes)).astype(dt)
+            xsd = xd if op != "*" else gpu.ROCArray.from_host(xs)
+            got = gpu.accumulate(op, xsd, dims=2, init=None).to_host()
+            ref = orc.accumulate(op, xs, axis=1)
+            if dt.kind == "i" or op in ("max", "min"):
+                assert np.array_equal(got.astype(np.float64), np.asarray(ref, dtype=np.float64)), (sizes, dt, op)
+            else:
+                assert_close(got, ref, 1e-2 if dt.itemsize == 2 else 1e-5, (sizes, dt, op))
+        seed = dt.type(2)
+        got = gpu.accumulate("+", xd, dims=2, init=seed).to_host()
+        ref = orc.accumulate("+", x, axis=1, init=seed)
+        if dt.kind == "i":
+            assert np.array_equal(got, ref)
+        else:
+            assert_close(got, ref, 1e-2 if dt.itemsize == 2 else 1e-5, (sizes, dt, "seeded"))
+        if dt == np.int32:      # exclusive form: shifted by one row, starting from the seed
+            out = gpu.ROCArray(dt, sizes)
+            gpu.accumulate_("+", out, xd, dims=2, init=dt.type(0), inclusive=False)
+            incl = np.cumsum(x, axis=1, dtype=dt)
+            excl = np.concatenate([np.zeros_like(incl[:, :1]), incl[:, :-1]], axis=1)
+            assert np.array_equal(out.to_host(), excl)
+    # a destination view that starts at an odd element: scalar column access
+    big = gpu.zeros(np.float32, sizes[0] * int(np.prod(sizes[1:])) + 1)
+    dst = big.view(1, big.size).reshape(sizes)
+    src = gpu.ROCArray.from_host(rng.random(sizes).astype(np.float32))
+    gpu.accumulate_("+", dst, src, dims=2)
+    assert_close(dst.to_host(), orc.accumulate("+", src.to_host(), axis=1), 1e-5)
