@@ -1,7 +1,7 @@
 // accumulate! / cumsum / cumprod: B[i] = op(B[i-1], A[i]) along one dimension.
 //
 // Takes the place of AK.accumulate! as called from src/kernels/accumulate.jl:1-8 of the
-// reference.  Three kernels share one descriptor protocol (aggregate / inclusive-prefix words
+// reference.  Four kernels share one descriptor protocol (aggregate / inclusive-prefix words
 // that successors poll):
 //  * long dense vectors: persistent two-pass segment scan (scan_segment_kernel).  A block reduces
 //    a 16-48 KiB segment from HBM, publishes its aggregate, resolves the prefix with one
@@ -10,7 +10,9 @@
 //  * everything else with enough work per column: one tile of 1024 16-byte vectors per block,
 //    chained scan with decoupled look-back, 256 predecessor descriptors per round; tiles take
 //    their index from an atomic ticket so that a tile's predecessors are always running;
-//  * very short columns and wide strided layouts: one thread per column (already coalesced).
+//  * long scans down a strided dimension (dims > 1 with at least a warp of columns): tiles of
+//    32*VEC columns x 128 rows chained along the scanned dimension, vector-valued descriptors;
+//  * very short columns and narrow strided layouts: one thread per column.
 // Every wait is bounded: a block that runs out of its poll budget latches B200_LOOKBACK_TIMEOUT
 // in the device's error word and leaves; other waiters notice the latched word and leave too.
 //
@@ -634,16 +636,16 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
 
 // ---- scan along a strided dimension (K > 1) -----------------------------------------------------------
 // cumsum(A; dims=2) and friends: neighbouring memory holds neighbouring COLUMNS, the scan runs
-// down the rows with stride K.  A block takes a tile of 32*VEC columns x 64 rows: a warp reads
-// row segments of 512 bytes (coalesced), every thread scans its VEC columns down the 8 rows of its
-// warp with 8 independent loads in flight, the 8 warps are stitched through shared memory, and
+// down the rows with stride K.  A block takes a tile of 32*VEC columns x 128 (64) rows: a warp reads
+// row segments of 512 bytes (coalesced), every thread scans its VEC columns down the 16 (8) rows of
+// its warp with that many independent loads in flight, the 8 warps are stitched through shared memory, and
 // tiles below each other are chained with the same aggregate / inclusive-prefix protocol as the
 // 1-D scans - here the published value is a vector (one entry per column of the strip).  Tickets
 // hand tiles out row-band by row-band, so the tile above a tile was handed out a whole band
 // earlier and its prefix is normally waiting; HBM sees one read and one write per element.
 constexpr int kSsWarps = 8;
-constexpr int kSsRows = 8;                          // rows per warp
-constexpr int kSsLY = kSsWarps * kSsRows;           // rows per tile
+// rows per warp: 64 values per thread whatever the vector width (16 rows of 4 floats, 8 rows of 8 halves)
+__host__ __device__ constexpr int ss_rows(int vec) { return vec >= 8 ? 8 : 16; }
 
 struct StridedScanPlan {
     int64_t K, L, M;
@@ -662,6 +664,7 @@ scan_strided_kernel(const T* A, T* B, StridedScanPlan pl, uint32_t* flags, typen
     using Acc = typename ScanAcc<T>::type;
     using VT = Vec<T, VEC>;
     constexpr int KX = 32 * VEC;                    // columns per strip
+    constexpr int kSsRows = ss_rows(VEC), kSsLY = kSsWarps * kSsRows;
     __shared__ Acc s_tot[kSsWarps][KX];
     __shared__ Acc s_pref[KX];
     __shared__ long long s_tile;
@@ -797,6 +800,7 @@ template <typename T, int OP, int VEC>
 static int32_t launch_scan_strided(b200_stream_t st, const void* A, void* B, const ScanPlan& pl) {
     using Acc = typename ScanAcc<T>::type;
     constexpr int KX = 32 * VEC;
+    constexpr int kSsLY = kSsWarps * ss_rows(VEC);
     StridedScanPlan sp{};
     sp.K = pl.K; sp.L = pl.L; sp.M = pl.M;
     sp.S = (pl.K + KX - 1) / KX;
