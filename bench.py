@@ -253,6 +253,42 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
         for d in (1, 2):
             rec(f"mat_cumsum_dims{d}_8192_f32", 8 * m * m, time_loop(pkg, st, pkg.accumulate_prepared("+", Bm, A, dims=d), reps(10)))
         del A, Bm
+    # the reference's own benchmark shapes (perf/array.jl:1-17,67-120,144-145): 512 x 1000 and
+    # 3 x 1 000 000 Float32 / Int64.  Latency-bound sizes; reported as time per call.  The one number
+    # the reference's tree holds for this set: accumulate(+, 3x1e6 Float32; dims=1) 70.5 us on gfx1100.
+    if want("ref"):
+        def lat(name, fn, bytes_):
+            ms = time_loop(pkg, st, fn, reps(200))
+            out[name] = {"us": round(ms * 1e3, 2), "GB/s": round(bytes_ / ms / 1e6, 1)}
+        for dt, tag in ((np.float32, "f32"), (np.int64, "i64")):
+            isz = np.dtype(dt).itemsize
+            def gen(shape):
+                a = pkg.ROCArray(dt, shape)
+                if dt == np.float32:
+                    return R.fill_random_(a, R.UNIFORM01, seed=7)
+                return R.fill_random_(a, R.INTEGERS, seed=7, lo=-10, hi=10)
+            mat, lng = gen((512, 1000)), gen((3, 1_000_000))
+            vec = mat.reshape(512_000)
+            o_mat, o_lng, o_vec = pkg.ROCArray(dt, (512, 1000)), pkg.ROCArray(dt, (3, 1_000_000)), pkg.ROCArray(dt, 512_000)
+            lat(f"ref_accumulate_1d_{tag}", pkg.accumulate_prepared("+", o_vec, vec), 2 * isz * 512_000)
+            for d in (1, 2):
+                lat(f"ref_accumulate_512x1000_dims{d}_{tag}", pkg.accumulate_prepared("+", o_mat, mat, dims=d), 2 * isz * 512_000)
+                lat(f"ref_accumulate_3x1e6_dims{d}_{tag}", pkg.accumulate_prepared("+", o_lng, lng, dims=d), 2 * isz * 3_000_000)
+            rdt = dt
+            r0 = pkg.ROCArray(rdt, (1, 1))
+            lat(f"ref_reduce_1d_{tag}", pkg.mapreduce_prepared("identity", "+", pkg.ROCArray(rdt, 1), vec, init=dt(0)), isz * 512_000)
+            lat(f"ref_reduce_512x1000_dims1_{tag}", pkg.mapreduce_prepared("identity", "+", pkg.ROCArray(rdt, (1, 1000)), mat, init=dt(0)), isz * 512_000)
+            lat(f"ref_reduce_512x1000_dims2_{tag}", pkg.mapreduce_prepared("identity", "+", pkg.ROCArray(rdt, (512, 1)), mat, init=dt(0)), isz * 512_000)
+            lat(f"ref_reduce_3x1e6_dims1_{tag}", pkg.mapreduce_prepared("identity", "+", pkg.ROCArray(rdt, (1, 1_000_000)), lng, init=dt(0)), isz * 3_000_000)
+            lat(f"ref_reduce_3x1e6_dims2_{tag}", pkg.mapreduce_prepared("identity", "+", pkg.ROCArray(rdt, (3, 1)), lng, init=dt(0)), isz * 3_000_000)
+            lat(f"ref_mapreduce_x+1_1d_{tag}", pkg.mapreduce_prepared(None, "+", r0.reshape(1), vec.dot + dt(1), init=dt(0)), isz * 512_000)
+            if dt == np.float32:
+                lat("ref_broadcast_fill_512x1000_f32", pkg.broadcast.prepared(o_mat, np.float32(0)), isz * 512_000)
+                keys = pkg.ROCArray(dt, 512_000)
+                def sort_once(_k=keys, _v=vec):
+                    pkg.copyto_(_k, _v); pkg.sort_(_k)
+                lat("ref_sort_512000_f32(copy+sort)", sort_once, 2 * isz * 512_000)
+            del mat, lng, vec, o_mat, o_lng, o_vec
     # config 3: 2^28 scans
     if want("c3") or want("c4_sort"):
         n = (1 << 28) >> shrink
