@@ -87,7 +87,7 @@ def test_int32_scan_is_deterministic_and_exact(gpu, orc):
     assert all(np.array_equal(outs[0], o) for o in outs[1:])
 
 
-def test_ring_kernel_small_types_and_variants(gpu, orc):
+def test_segment_kernel_small_types_and_variants(gpu, orc):
     """Long vectors of 16-bit and 64-bit elements, exclusive mode, device-resident carry, max-scan."""
     n = (1 << 21) + 64
     alt = np.where(np.arange(n) % 2 == 0, 1.0, -1.0)
