@@ -40,6 +40,7 @@ _DT2NP = {v: k for k, v in _NP2DT.items()}
 # opcodes
 OP_LEAF, OP_CONVERT, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_MULADD, OP_ABS, OP_ABS2, OP_EXP, OP_MAX, OP_MIN, OP_NEG = range(13)
 RED_ADD, RED_MUL, RED_MAX, RED_MIN = range(4)
+PEER_HOST, PEER_VMM, PEER_IPC = range(3)
 
 MAX_DIMS, MAX_LEAVES, MAX_PROGRAM = 8, 8, 64
 
@@ -111,6 +112,7 @@ SIGNATURES = {
     "b200_stream_wrap": [_i32, _vp, _P(_vp)],
     "b200_stream_destroy": [_vp],
     "b200_stream_sync": [_vp],
+    "b200_stream_release_scratch": [_vp],
     "b200_stream_query": [_vp],
     "b200_stream_device": [_vp, _P(_i32)],
     "b200_stream_raw": [_vp, _P(_vp)],
@@ -156,13 +158,16 @@ SIGNATURES = {
     "b200_graph_exec_update": [_vp, _vp, _P(C.c_int32)],
     "b200_fill_random": [_vp, _P(Tensor), _i32, _u64, _u64, _u64, _i64, _i64],
     "b200_selftest_wait_timeout": [_vp, C.c_uint32],
-    "b200_peer_create": [_i32, _i32, _i32, _P(_vp), C.c_char_p],
+    "b200_peer_create": [_i32, _i32, _i32, _i32, _P(_vp), C.c_char_p],
     "b200_peer_connect": [_vp, C.c_char_p],
+    "b200_peer_set_poll_budget": [_vp, C.c_uint32],
+    "b200_peer_info": [_vp, _P(_i32), _P(_u64)],
     "b200_peer_destroy": [_vp],
     "b200_mapreduce_allreduce": [_vp, _vp, _P(Tensor), _P(_i64), _i32, _P(Leaf), _i32, C.c_char_p, _i32, _i32, _vp],
     "b200_comm_unique_id": [C.c_char_p],
     "b200_comm_init_rank": [_P(_vp), _i32, _i32, C.c_char_p, _i32],
     "b200_comm_destroy": [_vp],
+    "b200_comm_check": [_vp, _vp, _i32],
     "b200_allreduce": [_vp, _vp, _sz, _i32, _i32, _vp],
     "b200_allgather": [_vp, _vp, _vp, _sz, _i32, _vp],
 }

@@ -12,7 +12,7 @@ import ctypes as C
 import numpy as np
 
 from ._lib import check, lib
-from .array import ROCArray, copyto_
+from .array import ROCArray, copyto_, with_managed
 from .mapreduce import _op_code
 from .runtime import Stream, current_stream
 
@@ -36,9 +36,12 @@ def accumulate_(op, B: ROCArray, A: ROCArray, init=_ZERO, dims=None, inclusive: 
     init_buf = None if init is None else np.asarray(init, dtype=A.dtype).tobytes()
     # the scan kernels want dense operands: wrapped ones (views, permuted dims) go through a dense
     # temporary, one strided copy in and one out
-    Ad, Bd = A.dense(), (B if B.is_contiguous else B.similar())
+    st = stream or current_stream()
+    Ad = A if A.is_contiguous else A.copy(st)
+    Bd = B if B.is_contiguous else B.similar(stream=st)
     tb, ta = Bd.tensor(), Ad.tensor()
-    check(lib.b200_accumulate((stream or current_stream()).handle, C.byref(tb), C.byref(ta), _op_code(op),
+    with_managed(st, Bd, Ad)
+    check(lib.b200_accumulate(st.handle, C.byref(tb), C.byref(ta), _op_code(op),
                               init_buf, dims - 1, 1 if inclusive else 0))
     if Bd is not B:
         copyto_(B, Bd, stream)
@@ -70,5 +73,6 @@ def prepared(op, B: ROCArray, A: ROCArray, init=_ZERO, dims: int = 1, stream: St
     fn, opc = lib.b200_accumulate, _op_code(op)
 
     def launch(_keep=(A, B, st)):
+        with_managed(st, B, A)
         check(fn(st.handle, C.byref(tb), C.byref(ta), opc, init_buf, dims - 1, 1))
     return launch

@@ -10,32 +10,66 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import threading
 
 import numpy as np
 
 from . import _lib
 from ._lib import check, lib
 from .memory import current_cache, pool_alloc, pool_free
-from .runtime import Stream, current_stream
+from .runtime import Event, Stream, current_stream
 
 
 class _Managed:
-    """Reference-counted device buffer tied to the stream that owns it (the role of
-    ``Managed`` + ``DataRef``, src/memory.jl:408-418)."""
+    """Reference-counted device buffer with the reference's ownership record (``Managed`` +
+    ``DataRef``, src/memory.jl:408-418): the stream that touched it last and whether work on that
+    stream may still be using it (``dirty``).  An operation on another stream first takes the
+    buffer over (:meth:`take_ownership`), and the stream-ordered free goes to the last owner."""
 
-    __slots__ = ("ptr", "nbytes", "stream", "freed", "cached", "__weakref__")
+    __slots__ = ("ptr", "nbytes", "stream", "dirty", "freed", "cached", "_lock", "__weakref__")
 
     def __init__(self, nbytes: int, stream: Stream):
         self.ptr, self.freed = 0, True          # a failed allocation must leave a harmless object
         self.nbytes = nbytes
         self.stream = stream
+        self.dirty = True
+        self._lock = threading.Lock()
         cache = current_cache()                 # GPUArrays.cached_alloc hook (src/array.jl:27-30)
         self.cached = cache is not None and nbytes > 0
         if self.cached:
-            self.ptr = cache.take((stream.device, nbytes), lambda: pool_alloc(nbytes, stream))
+            # buffers are only handed back to requests on the stream that used them last
+            key = (stream.device, getattr(stream.handle, "value", stream.handle), nbytes)
+            self.ptr = cache.take(key, lambda: pool_alloc(nbytes, stream))
         else:
             self.ptr = pool_alloc(nbytes, stream)
         self.freed = False
+
+    def take_ownership(self, stream: Stream) -> None:
+        """``take_ownership!(managed; stream)`` (src/memory.jl:431-446).  When the buffer was last
+        used on another stream and that work may still be running, the new stream is made to wait
+        for it: an event recorded on the old stream and a wait on the new one - the same ordering
+        as the reference's ``synchronize(old stream)`` without blocking the host (streams of
+        different devices do block)."""
+        if self.stream is stream:
+            self.dirty = True
+            return
+        with self._lock:
+            old = self.stream
+            if (self.dirty and old.handle is not None and stream.handle is not None
+                    and old.handle.value != stream.handle.value):
+                if old.device == stream.device:
+                    stream.wait(Event(old.device).record(old))
+                else:
+                    old.synchronize()
+            self.stream = stream
+            self.dirty = True
+
+    def synchronize(self) -> None:
+        """``synchronize(managed)`` (src/memory.jl:422-429): wait until the last owner is done."""
+        with self._lock:
+            if self.dirty and self.stream.handle is not None:
+                self.stream.synchronize()
+                self.dirty = False
 
     def free(self) -> None:
         if self.cached:                         # the allocation cache owns the memory
@@ -44,13 +78,23 @@ class _Managed:
         if not self.freed and self.ptr:
             self.freed = True
             try:
+                # the last owner's stream; a stale one falls back to the current stream (src/memory.jl:531-536)
                 st = self.stream if self.stream.handle is not None else current_stream()
-                pool_free(self.ptr, st)   # stale owner: fall back to the current stream (src/memory.jl:531-536)
+                pool_free(self.ptr, st)
             except Exception:
                 pass
 
     def __del__(self):
         self.free()
+
+
+def with_managed(stream: Stream, *arrays) -> Stream:
+    """``with_managed(f, managed; stream)`` (src/memory.jl:460-469): every buffer an operation
+    reads or writes is handed to the launch stream before the launch.  Returns `stream`."""
+    for a in arrays:
+        if a is not None:
+            a.buf.take_ownership(stream)
+    return stream
 
 
 class ROCArray:
@@ -148,7 +192,7 @@ class ROCArray:
             copyto_(self, ROCArray.from_host(a.reshape(self.dims, order="F"), stream), stream)
             return self
         flat = np.ascontiguousarray(a.reshape(-1, order="F"))
-        st = stream or current_stream()
+        st = with_managed(stream or current_stream(), self)
         if flat.nbytes:
             check(lib.b200_memcpy_async(C.c_void_p(self.ptr), C.c_void_p(flat.ctypes.data), flat.nbytes, st.handle))
             st.synchronize()   # pageable source must stay alive until the copy is done
@@ -159,10 +203,11 @@ class ROCArray:
         if not self.is_contiguous:
             return self.copy().to_host(stream)
         out = np.empty(self.size, dtype=self.dtype)
-        st = stream or current_stream()
+        st = with_managed(stream or current_stream(), self)
         if out.nbytes:
             check(lib.b200_memcpy_async(C.c_void_p(out.ctypes.data), C.c_void_p(self.ptr), out.nbytes, st.handle))
         st.synchronize()
+        self.buf.dirty = False
         return out.reshape(self.dims, order="F")
 
     def item(self):
@@ -170,15 +215,15 @@ class ROCArray:
             raise ValueError("item() needs exactly one element")
         return self.to_host().reshape(-1)[0]
 
-    def similar(self, dtype=None, dims=None) -> "ROCArray":
-        """``similar(A, T, dims)`` (src/array.jl:109)."""
+    def similar(self, dtype=None, dims=None, stream: Stream | None = None) -> "ROCArray":
+        """``similar(A, T, dims)`` (src/array.jl:109): storage from the pool on the stream in use."""
         return ROCArray(self.dtype if dtype is None else dtype, self.dims if dims is None else dims,
-                        stream=self.buf.stream)
+                        stream=stream or current_stream())
 
-    def copy(self) -> "ROCArray":
+    def copy(self, stream: Stream | None = None) -> "ROCArray":
         """``copy(A)`` (src/array.jl:268-272): device-to-device."""
-        out = self.similar()
-        copyto_(out, self)
+        out = self.similar(stream=stream)
+        copyto_(out, self, stream)
         return out
 
     def reshape(self, *dims) -> "ROCArray":
@@ -266,8 +311,8 @@ class ROCArray:
             return self
         if self.size:
             bits = int.from_bytes(np.asarray(value, dtype=self.dtype).tobytes().ljust(8, b"\0"), "little")
-            check(lib.b200_memset_async(C.c_void_p(self.ptr), bits, self.itemsize, self.size,
-                                        (stream or current_stream()).handle))
+            st = with_managed(stream or current_stream(), self)
+            check(lib.b200_memset_async(C.c_void_p(self.ptr), bits, self.itemsize, self.size, st.handle))
         return self
 
     def unsafe_free_(self) -> None:
@@ -296,8 +341,8 @@ def copyto_(dest: ROCArray, src: ROCArray, stream: Stream | None = None) -> ROCA
         materialize_(dest, Broadcasted.leaf(src), stream)
         return dest
     if dest.size:
-        check(lib.b200_memcpy_async(C.c_void_p(dest.ptr), C.c_void_p(src.ptr), src.nbytes,
-                                    (stream or current_stream()).handle))
+        st = with_managed(stream or current_stream(), dest, src)
+        check(lib.b200_memcpy_async(C.c_void_p(dest.ptr), C.c_void_p(src.ptr), src.nbytes, st.handle))
     return dest
 
 

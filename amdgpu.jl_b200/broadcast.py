@@ -17,7 +17,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import check, lib
-from .array import ROCArray
+from .array import ROCArray, with_managed
 from .runtime import Stream, current_stream
 
 _FLOATS = (_lib.F16, _lib.BF16, _lib.F32, _lib.F64)
@@ -192,7 +192,7 @@ class Broadcasted:
 
     def materialize(self, stream: Stream | None = None) -> ROCArray:
         """``Base.materialize(bc)``: allocate with ``similar`` (src/broadcast.jl:26-30), then fill."""
-        out = ROCArray(_lib.dtype_numpy(self.dtype), self.shape())
+        out = ROCArray(_lib.dtype_numpy(self.dtype), self.shape(), stream=stream)
         return materialize_(out, self, stream)
 
 
@@ -204,9 +204,10 @@ def materialize_(dest: ROCArray, bc, stream: Stream | None = None) -> ROCArray:
     if len(src_shape) > dest.ndim or any(
             e != 1 and e != dest.dims[d] for d, e in enumerate(src_shape)):
         raise ValueError(f"DimensionMismatch: destination {dest.dims} cannot hold broadcast of shape {src_shape}")
-    code, leaves, nleaves, _keep = bc.flatten()
+    code, leaves, nleaves, keep = bc.flatten()
     t = dest.tensor()
-    check(lib.b200_broadcast((stream or current_stream()).handle, C.byref(t), leaves, nleaves, code, len(code) // 2))
+    st = with_managed(stream or current_stream(), dest, *keep)
+    check(lib.b200_broadcast(st.handle, C.byref(t), leaves, nleaves, code, len(code) // 2))
     return dest
 
 
@@ -241,6 +242,7 @@ def prepared(dest: ROCArray, bc, stream: Stream | None = None):
     fn, ninstr = lib.b200_broadcast, len(code) // 2
 
     def launch(_keep=(keep, dest, st)):
+        with_managed(st, dest, *keep)
         check(fn(st.handle, C.byref(t), leaves, nleaves, code, ninstr))
     return launch
 

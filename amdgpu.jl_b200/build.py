@@ -15,9 +15,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build"
-LIB = HERE / "lib" / os.environ.get("B200_LIB_NAME", "libb200arrays.so")
-if "B200_LIB_NAME" in os.environ:      # variant builds (tuning experiments) keep their own objects
-    OBJ = HERE / "build" / os.environ["B200_LIB_NAME"].replace(".", "_")
+LIB = HERE / "lib" / "libb200arrays.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -26,7 +24,6 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-fmad=false",            # separate multiply/add stay separately rounded (Base semantics)
     "-Xptxas", "-v" if os.environ.get("B200_PTXAS_V") else "-O3",
-    *os.environ.get("B200_EXTRA_NVCC_FLAGS", "").split(),
 ]
 
 

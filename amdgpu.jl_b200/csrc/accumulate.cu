@@ -18,7 +18,7 @@
 //
 // The array is collapsed to (K, L, M) around the scanned dimension: K*M independent columns of
 // L elements with element stride K.
-#include "program.cuh"
+#include "scan_common.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -32,39 +32,6 @@ constexpr int kScanThreads = 256;
 constexpr int kScanVecs = 4;               // 16-byte vectors per thread
 constexpr int kScanWarps = kScanThreads / 32;
 static_assert(kScanVecs * kScanWarps == 32, "warp totals must fill exactly one warp");
-
-enum : uint32_t { FLAG_EMPTY = 0, FLAG_AGGREGATE = 1, FLAG_PREFIX = 2 };
-
-template <typename Acc, int OP>
-__device__ __forceinline__ Acc scan_identity() {
-    if constexpr (OP == B200_RED_ADD) return Acc(0);
-    else if constexpr (OP == B200_RED_MUL) return Acc(1);
-    else if constexpr (OP == B200_RED_MAX) {
-        if constexpr (std::is_floating_point<Acc>::value) return -std::numeric_limits<Acc>::infinity();
-        else return std::numeric_limits<Acc>::lowest();
-    } else {
-        if constexpr (std::is_floating_point<Acc>::value) return std::numeric_limits<Acc>::infinity();
-        else return std::numeric_limits<Acc>::max();
-    }
-}
-template <typename Acc, int OP>
-__device__ __forceinline__ Acc scan_apply(Acc a, Acc b) {
-    using A = Arith<Acc>;
-    if constexpr (OP == B200_RED_ADD) return A::add(a, b);
-    else if constexpr (OP == B200_RED_MUL) return A::mul(a, b);
-    else if constexpr (OP == B200_RED_MAX) return A::max(a, b);
-    else return A::min(a, b);
-}
-
-template <typename T> struct ScanAcc { using type = T; };
-template <> struct ScanAcc<__half> { using type = float; };
-template <> struct ScanAcc<__nv_bfloat16> { using type = float; };
-template <typename T> __device__ __forceinline__ typename ScanAcc<T>::type scan_up(T v) { return v; }
-template <> __device__ __forceinline__ float scan_up<__half>(__half v) { return __half2float(v); }
-template <> __device__ __forceinline__ float scan_up<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <typename T> __device__ __forceinline__ T scan_down(typename ScanAcc<T>::type v) { return (T)v; }
-template <> __device__ __forceinline__ __half scan_down<__half>(float v) { return __float2half_rn(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 scan_down<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 // ---- tile descriptors ---------------------------------------------------------------------------------
 // 4-byte accumulators: one 64-bit word {flag:32 | value:32}, written and read with single accesses.
@@ -116,36 +83,6 @@ struct TileState<Acc, false> {
     }
 };
 
-struct ScanPlan {
-    int64_t K, L, M;         // columns c = (k, m): base k + K*L*m, element stride K
-    int64_t tiles_per_col;
-    int64_t ntiles;
-    int32_t vec_ok;          // K == 1 and every column start is 16-byte aligned in A and B
-    int32_t inclusive;
-    int32_t has_init;
-    uint32_t max_polls;
-    uint64_t init;           // accumulator class bits (has_init == 1)
-    const void* init_dev;    // one element of the array's type in device memory (has_init == 2)
-};
-
-template <typename T>
-__device__ __forceinline__ typename ScanAcc<T>::type scan_seed(const ScanPlan& pl) {
-    using Acc = typename ScanAcc<T>::type;
-    if (pl.has_init == 2) return scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev));
-    return as_c<Acc, uint64_t>(pl.init);
-}
-
-// Inclusive warp scan over lanes; returns the inclusive value.
-template <typename Acc, int OP>
-__device__ __forceinline__ Acc warp_scan_inclusive(Acc v, int lane) {
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        Acc o = __shfl_up_sync(0xffffffffu, v, off);
-        if (lane >= off) v = scan_apply<Acc, OP>(o, v);
-    }
-    return v;
-}
-
 template <typename T, int OP>
 __global__ void __launch_bounds__(kScanThreads)
 scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned int* ticket, int32_t* err_word) {
@@ -167,7 +104,6 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
     state.bind(state_mem, pl.ntiles);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    B200_PHASE_BEGIN();
     if (tid == 0) {
         const unsigned int t = atomicAdd(ticket, 1u);
         if ((int64_t)t == pl.ntiles - 1) *ticket = 0;   // nobody takes a ticket after the last tile
@@ -205,7 +141,6 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
             }
     }
 
-    B200_PHASE_MARK(0);   // ticket + loads issued
     // ---- thread-local inclusive scans per vector, then warp scans of the vector totals
     Acc lane_ex[kScanVecs];
 #pragma unroll
@@ -220,7 +155,6 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
     }
     __syncthreads();
 
-    B200_PHASE_MARK(1);   // load latency + local scan
     // ---- warp 0: scan the 32 warp totals; the tile aggregate goes to shared memory
     if (warp == 0) {
         const Acc wt = s_warp[lane];
@@ -308,7 +242,6 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
         }
     }
     __syncthreads();
-    B200_PHASE_MARK(2);   // look-back
     if (s_abort) return;
 
     // ---- apply offsets and store
@@ -337,7 +270,6 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
             }
         }
     }
-    B200_PHASE_MARK(3);   // offsets + stores issued
 }
 
 // ---- persistent two-pass scan over L2-sized segments ----------------------------------------------------
@@ -387,7 +319,6 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
     uint4* dst = reinterpret_cast<uint4*>(B);
     if (tid == 0) s_abort = 0;
     __syncthreads();
-    B200_PHASE_BEGIN();
     const uint64_t keep = l2_policy_keep(), stream = l2_policy_stream();
 
     // Block-wide reduction of the per-thread pass-1 accumulators and publication of the segment's
@@ -527,11 +458,9 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
         reduce_segment(seg + G, acc);
         agg_next = publish_aggregate(seg + G, acc);
     }
-    B200_PHASE_MARK(4);   // prologue
 
     while (true) {
         if (!lookback(seg, agg_cur)) break;
-        B200_PHASE_MARK(6);   // look-back
         const int64_t ahead = seg + 2 * G;                 // pass 1 runs two segments ahead
         const bool has_ahead = ahead < pl.nsegs;
         const int64_t v0 = seg * pl.seg_vecs;
@@ -623,7 +552,6 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
             __syncthreads();      // s_warp / s_wex / s_total are reused by the next sub-tile
         }
         cp_async_wait<0>();
-        B200_PHASE_MARK(5);   // fused pass 2 (current) + pass 1 (two ahead)
         Acc agg_ahead = scan_identity<Acc, OP>();
         if (has_ahead) agg_ahead = publish_aggregate(ahead, acc);
         seg += G;
@@ -848,6 +776,16 @@ scan_column_thread_kernel(const T* A, T* B, ScanPlan pl) {
     }
 }
 
+template <typename T> constexpr int32_t scan_dtype_code();
+template <> constexpr int32_t scan_dtype_code<float>() { return B200_F32; }
+template <> constexpr int32_t scan_dtype_code<double>() { return B200_F64; }
+template <> constexpr int32_t scan_dtype_code<int32_t>() { return B200_I32; }
+template <> constexpr int32_t scan_dtype_code<int64_t>() { return B200_I64; }
+template <> constexpr int32_t scan_dtype_code<uint32_t>() { return B200_U32; }
+template <> constexpr int32_t scan_dtype_code<uint64_t>() { return B200_U64; }
+template <> constexpr int32_t scan_dtype_code<__half>() { return B200_F16; }
+template <> constexpr int32_t scan_dtype_code<__nv_bfloat16>() { return B200_BF16; }
+
 template <typename T, int OP>
 static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl) {
     using Acc = typename ScanAcc<T>::type;
@@ -869,6 +807,10 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         return B200_OK;
     }
     if (ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {
+        // long dense vectors: the one-pass ring kernel where it applies (4-byte accumulators),
+        // else the two-pass segment kernel below
+        const int32_t ring = launch_scan_ring(st, scan_dtype_code<T>(), OP, A, B, pl);
+        if (ring != B200_UNSUPPORTED) return ring;
         SegPlan sp{};
         sp.nvec = pl.L * (int64_t)sizeof(T) / 16;
         int64_t grid = resident_blocks(scan_segment_kernel<T, OP>, kSegThreads, 0, st->dev);
@@ -1001,9 +943,11 @@ static int32_t launch_scan_static_op(b200_stream_t st, const void* A, void* B, c
 
 using namespace b200;
 
-static int32_t accumulate_common(b200_stream_t st, const b200_tensor* B, const b200_tensor* A, int32_t op,
-                                 const void* init, const void* init_dev, int32_t dim, int32_t inclusive) {
-    B200_TRY(enter(st));
+// Validation and plan shared by every accumulate entry point: checks the descriptors, collapses
+// the shape to (K, L, M) around the scanned dimension and folds the seed into the plan.  `*empty`
+// is set for arrays without elements (nothing to launch).
+static int32_t scan_plan(const b200_tensor* B, const b200_tensor* A, int32_t op, const void* init, const void* init_dev,
+                         int32_t dim, int32_t inclusive, ScanPlan* out, bool* empty) {
     B200_TRY(check_tensor(B, "accumulate destination"));
     B200_TRY(check_tensor(A, "accumulate source"));
     if (op < 0 || op >= B200_RED_COUNT) return fail(B200_UNSUPPORTED, "accumulate: unknown operator %d", op);
@@ -1013,10 +957,9 @@ static int32_t accumulate_common(b200_stream_t st, const b200_tensor* B, const b
         if (A->shape[d] != B->shape[d]) return fail(B200_INVALID_ARG, "accumulate: source and destination shapes differ");
     if (!tensor_is_contiguous(A) || !tensor_is_contiguous(B))
         return fail(B200_UNSUPPORTED, "accumulate: operands must be dense column-major arrays");
-    const int64_t n = tensor_numel(A);
-    if (n == 0) return B200_OK;
+    *empty = tensor_numel(A) == 0;
+    if (*empty) return B200_OK;
     if (dim < 0) return fail(B200_INVALID_ARG, "accumulate: negative dimension");
-
     ScanPlan pl{};
     pl.K = 1; pl.L = 1; pl.M = 1;
     for (int d = 0; d < A->ndim; ++d) {
@@ -1037,18 +980,33 @@ static int32_t accumulate_common(b200_stream_t st, const b200_tensor* B, const b
         long v = atol(e);
         if (v > 0) pl.max_polls = (uint32_t)v;
     }
-    int32_t s;
-    switch (A->dtype) {
-        case B200_F32: s = launch_scan_op<float>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_F64: s = launch_scan_op<double>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_I32: s = launch_scan_op<int32_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_I64: s = launch_scan_op<int64_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_U32: s = launch_scan_op<uint32_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_U64: s = launch_scan_op<uint64_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_F16: s = launch_scan_op<__half>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_BF16: s = launch_scan_op<__nv_bfloat16>(st, A->ptr, B->ptr, pl, op); break;
-        default: return fail(B200_UNSUPPORTED, "accumulate: element type %d is not supported", A->dtype);
+    *out = pl;
+    return B200_OK;
+}
+
+#define B200_SCAN_DTYPE_SWITCH(LAUNCH)                                                                  \
+    switch (A->dtype) {                                                                                 \
+        case B200_F32: s = LAUNCH<float>(st, A->ptr, B->ptr, pl, op); break;                            \
+        case B200_F64: s = LAUNCH<double>(st, A->ptr, B->ptr, pl, op); break;                           \
+        case B200_I32: s = LAUNCH<int32_t>(st, A->ptr, B->ptr, pl, op); break;                          \
+        case B200_I64: s = LAUNCH<int64_t>(st, A->ptr, B->ptr, pl, op); break;                          \
+        case B200_U32: s = LAUNCH<uint32_t>(st, A->ptr, B->ptr, pl, op); break;                         \
+        case B200_U64: s = LAUNCH<uint64_t>(st, A->ptr, B->ptr, pl, op); break;                         \
+        case B200_F16: s = LAUNCH<__half>(st, A->ptr, B->ptr, pl, op); break;                           \
+        case B200_BF16: s = LAUNCH<__nv_bfloat16>(st, A->ptr, B->ptr, pl, op); break;                   \
+        default: return fail(B200_UNSUPPORTED, "accumulate: element type %d is not supported", A->dtype); \
     }
+
+static int32_t accumulate_common(b200_stream_t st, const b200_tensor* B, const b200_tensor* A, int32_t op,
+                                 const void* init, const void* init_dev, int32_t dim, int32_t inclusive) {
+    B200_TRY(enter(st));
+    StreamGuard guard(st);
+    ScanPlan pl{};
+    bool empty = false;
+    B200_TRY(scan_plan(B, A, op, init, init_dev, dim, inclusive, &pl, &empty));
+    if (empty) return B200_OK;
+    int32_t s;
+    B200_SCAN_DTYPE_SWITCH(launch_scan_op)
     B200_TRY(s);
     return finish(st, "b200_accumulate");
 }
@@ -1077,49 +1035,16 @@ extern "C" int32_t b200_accumulate_carry(b200_stream_t st, const b200_tensor* B,
 extern "C" int32_t b200_accumulate_noalloc(b200_stream_t st, const b200_tensor* B, const b200_tensor* A, int32_t op,
                                            const void* init, int32_t dim, int32_t inclusive) {
     B200_TRY(enter(st));
-    B200_TRY(check_tensor(B, "accumulate destination"));
-    B200_TRY(check_tensor(A, "accumulate source"));
-    if (op < 0 || op >= B200_RED_COUNT) return fail(B200_UNSUPPORTED, "accumulate: unknown operator %d", op);
-    if (A->dtype != B->dtype) return fail(B200_UNSUPPORTED, "accumulate: source and destination element types differ");
-    if (A->ndim != B->ndim) return fail(B200_INVALID_ARG, "accumulate: source and destination shapes differ");
-    for (int d = 0; d < A->ndim; ++d)
-        if (A->shape[d] != B->shape[d]) return fail(B200_INVALID_ARG, "accumulate: source and destination shapes differ");
-    if (!tensor_is_contiguous(A) || !tensor_is_contiguous(B))
-        return fail(B200_UNSUPPORTED, "accumulate: operands must be dense column-major arrays");
-    if (tensor_numel(A) == 0) return B200_OK;
-    if (dim < 0) return fail(B200_INVALID_ARG, "accumulate: negative dimension");
+    StreamGuard guard(st);
     ScanPlan pl{};
-    pl.K = 1; pl.L = 1; pl.M = 1;
-    for (int d = 0; d < A->ndim; ++d) {
-        if (d < dim) pl.K *= A->shape[d];
-        else if (d == dim) pl.L = A->shape[d];
-        else pl.M *= A->shape[d];
-    }
-    pl.inclusive = inclusive ? 1 : 0;
-    pl.has_init = init ? 1 : 0;
-    if (init) {
-        uint64_t bits = 0;
-        memcpy(&bits, init, dtype_size(A->dtype));
-        pl.init = scalar_to_class(A->dtype, bits);
-    }
-    pl.max_polls = 1u << 22;
+    bool empty = false;
+    B200_TRY(scan_plan(B, A, op, init, nullptr, dim, inclusive, &pl, &empty));
+    if (empty) return B200_OK;
     int32_t s;
-    switch (A->dtype) {
-        case B200_F32: s = launch_scan_static_op<float>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_F64: s = launch_scan_static_op<double>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_I32: s = launch_scan_static_op<int32_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_I64: s = launch_scan_static_op<int64_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_U32: s = launch_scan_static_op<uint32_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_U64: s = launch_scan_static_op<uint64_t>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_F16: s = launch_scan_static_op<__half>(st, A->ptr, B->ptr, pl, op); break;
-        case B200_BF16: s = launch_scan_static_op<__nv_bfloat16>(st, A->ptr, B->ptr, pl, op); break;
-        default: return fail(B200_UNSUPPORTED, "accumulate: element type %d is not supported", A->dtype);
-    }
+    B200_SCAN_DTYPE_SWITCH(launch_scan_static_op)
     B200_TRY(s);
     return finish(st, "b200_accumulate_noalloc");
 }
-
-B200_DEFINE_PHASE_READER(b200_debug_phases_scan)
 
 // Self-test of the bounded wait: runs ONE tile of the chained scan whose ticket says it is tile 1
 // while tile 0 never exists, with a poll budget of `polls`.  The block gives up after that many
@@ -1127,6 +1052,7 @@ B200_DEFINE_PHASE_READER(b200_debug_phases_scan)
 // context stays usable.  Nothing faults and nothing spins without a limit.
 extern "C" int32_t b200_selftest_wait_timeout(b200_stream_t st, uint32_t polls) {
     B200_TRY(enter(st));
+    StreamGuard guard(st);
     if (polls == 0 || polls > (1u << 20)) return fail(B200_INVALID_ARG, "poll budget must be in 1..2^20");
     constexpr int TILE = kScanThreads * kScanVecs * 4;
     void* scr = nullptr;

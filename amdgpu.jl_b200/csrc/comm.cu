@@ -9,8 +9,11 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <thread>
 
 struct b200_comm_s {
     ncclComm_t comm;
@@ -27,6 +30,8 @@ struct NcclApi {
     decltype(&ncclAllReduce) AllReduce = nullptr;
     decltype(&ncclAllGather) AllGather = nullptr;
     decltype(&ncclGetErrorString) GetErrorString = nullptr;
+    decltype(&ncclCommGetAsyncError) CommGetAsyncError = nullptr;
+    decltype(&ncclCommAbort) CommAbort = nullptr;
 };
 static NcclApi g_nccl;
 static std::mutex g_nccl_mu;
@@ -34,9 +39,11 @@ static std::mutex g_nccl_mu;
 static int32_t load_nccl() {
     std::lock_guard<std::mutex> lk(g_nccl_mu);
     if (g_nccl.handle) return B200_OK;
-    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    // B200_NCCL_LIB names the library to load instead of the system's (a path or a soname)
+    const char* names[] = {getenv("B200_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
     void* h = nullptr;
     for (const char* nm : names) {
+        if (!nm || !nm[0]) continue;
         h = dlopen(nm, RTLD_NOW | RTLD_GLOBAL);
         if (h) break;
     }
@@ -50,6 +57,8 @@ static int32_t load_nccl() {
     B200_SYM(AllReduce, "ncclAllReduce")
     B200_SYM(AllGather, "ncclAllGather")
     B200_SYM(GetErrorString, "ncclGetErrorString")
+    B200_SYM(CommGetAsyncError, "ncclCommGetAsyncError")
+    B200_SYM(CommAbort, "ncclCommAbort")
 #undef B200_SYM
     g_nccl.handle = h;
     return B200_OK;
@@ -99,7 +108,7 @@ extern "C" int32_t b200_comm_init_rank(b200_comm_t* out, int32_t nranks, int32_t
     if (!out || !id) return fail(B200_INVALID_ARG, "null argument");
     if (nranks < 1 || rank < 0 || rank >= nranks) return fail(B200_INVALID_ARG, "rank %d outside [0,%d)", rank, nranks);
     B200_TRY(load_nccl());
-    B200_CUDA(cudaSetDevice(dev));
+    if (dev >= 0) B200_CUDA(cudaSetDevice(dev));      // dev < 0: not bound to a device (health checks only)
     ncclUniqueId uid;
     memcpy(&uid, id, 128);
     ncclComm_t c;
@@ -110,15 +119,58 @@ extern "C" int32_t b200_comm_init_rank(b200_comm_t* out, int32_t nranks, int32_t
 
 extern "C" int32_t b200_comm_destroy(b200_comm_t comm) {
     if (!comm) return B200_OK;
-    cudaSetDevice(comm->dev);
-    ncclResult_t r = g_nccl.CommDestroy(comm->comm);
+    if (comm->dev >= 0) cudaSetDevice(comm->dev);
+    ncclResult_t r = comm->comm ? g_nccl.CommDestroy(comm->comm) : ncclSuccess;   // an aborted communicator is already gone
     delete comm;
     if (r != ncclSuccess) return nccl_fail(r, "ncclCommDestroy");
     return B200_OK;
 }
 
+// Failure detection for the collectives, on the host: NCCL reports a failed peer or transport
+// through ncclCommGetAsyncError, and a collective whose peer never arrives simply never ends.
+// This call watches both until the stream has drained or `timeout_ms` has passed; on an error or
+// a timeout it aborts the communicator (ncclCommAbort: the stuck kernel leaves the GPU, the
+// stream becomes usable again) and reports B200_NCCL_ERROR.  Afterwards the communicator only
+// accepts b200_comm_destroy.  The reference's closest relative is the one-second watchdog on a
+// stream that does not finish (src/hip/stream.jl:99-126).
+extern "C" int32_t b200_comm_check(b200_comm_t comm, b200_stream_t st, int32_t timeout_ms) {
+    if (!comm) return fail(B200_INVALID_ARG, "null communicator");
+    if (!comm->comm) return fail(B200_NCCL_ERROR, "the communicator was aborted");
+    if (st) {
+        B200_TRY(enter(st));
+        if (st->dev != comm->dev) return fail(B200_INVALID_ARG, "stream and communicator live on different devices");
+    }
+    const auto t0 = std::chrono::steady_clock::now();
+    while (true) {
+        ncclResult_t async = ncclSuccess;
+        ncclResult_t r = g_nccl.CommGetAsyncError(comm->comm, &async);
+        if (r != ncclSuccess) async = r;
+        if (async != ncclSuccess && async != ncclInProgress) {
+            g_nccl.CommAbort(comm->comm);
+            comm->comm = nullptr;
+            return nccl_fail(async, "a collective in flight (communicator aborted)");
+        }
+        bool done = true;
+        if (st) {
+            cudaError_t e = cudaStreamQuery(st->s);
+            if (e == cudaErrorNotReady) { cudaGetLastError(); done = false; }
+            else if (e != cudaSuccess) return cuda_fail(e, "cudaStreamQuery");
+        }
+        if (done && async == ncclSuccess) return B200_OK;
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms >= timeout_ms) {
+            if (!st && async == ncclInProgress) return B200_NOT_READY;
+            g_nccl.CommAbort(comm->comm);
+            comm->comm = nullptr;
+            return fail(B200_NCCL_ERROR, "collective did not finish within %d ms: a rank is missing or stuck (communicator aborted)", timeout_ms);
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+}
+
 extern "C" int32_t b200_allreduce(b200_comm_t comm, void* buf, size_t count, int32_t dtype, int32_t op, b200_stream_t st) {
     if (!comm) return fail(B200_INVALID_ARG, "null communicator");
+    if (!comm->comm) return fail(B200_NCCL_ERROR, "the communicator was aborted");
     B200_TRY(enter(st));
     if (st->dev != comm->dev) return fail(B200_INVALID_ARG, "stream and communicator live on different devices");
     if (op < 0 || op >= B200_RED_COUNT) return fail(B200_UNSUPPORTED, "allreduce: unknown operator %d", op);
@@ -131,6 +183,7 @@ extern "C" int32_t b200_allreduce(b200_comm_t comm, void* buf, size_t count, int
 
 extern "C" int32_t b200_allgather(b200_comm_t comm, const void* send, void* recv, size_t count, int32_t dtype, b200_stream_t st) {
     if (!comm) return fail(B200_INVALID_ARG, "null communicator");
+    if (!comm->comm) return fail(B200_NCCL_ERROR, "the communicator was aborted");
     B200_TRY(enter(st));
     if (st->dev != comm->dev) return fail(B200_INVALID_ARG, "stream and communicator live on different devices");
     ncclDataType_t dt;

@@ -11,6 +11,7 @@
 #include <stdint.h>
 #include <stddef.h>
 #ifndef __CUDACC_RTC__
+#include <mutex>
 #include <string>
 #include <vector>
 #endif
@@ -32,6 +33,22 @@ struct b200_stream_s {
     // if a later call needs a larger one).
     bool         scratch_in_graph;
     std::vector<void*> retired;
+    // Descriptor words of the one-pass scan: a buffer that only that kernel writes, every word
+    // tagged with the number of the launch that wrote it (`scan_epoch`), so that words left by
+    // earlier launches read as "empty" and no launch has to clear them first.
+    void*        scan_state = nullptr;
+    size_t       scan_state_bytes = 0;
+    uint32_t     scan_epoch = 0;
+    bool         scan_state_in_graph = false;
+    // Serialises host threads that issue operators on this stream: scratch handed to one call
+    // must stay valid until that call has enqueued its kernels.
+    std::recursive_mutex mu;
+};
+
+// Held by an operator from validation to its last launch.
+struct StreamGuard {
+    explicit StreamGuard(b200_stream_t st) : lk(st->mu) {}
+    std::lock_guard<std::recursive_mutex> lk;
 };
 
 struct b200_event_s {
@@ -81,6 +98,14 @@ int32_t enter(b200_stream_t st);
 // (the last block to take a ticket resets it); `counters` receives that region.
 constexpr size_t kCounterBytes = 64 * 1024;
 int32_t scratch(b200_stream_t st, size_t bytes, void** out, unsigned int** counters = nullptr);
+// Descriptor storage for the one-pass scan (see b200_stream_s::scan_state): at least `bytes` after
+// a 256-byte header whose first word is the tile ticket (zero between launches).  `epoch` receives
+// this launch's tag (1 .. 2^30-1).  `*must_clear` is set when the stream is being captured: a
+// replayed graph repeats its tag, so such a launch clears header and descriptors itself first.
+constexpr size_t kScanStateHeader = 256;
+int32_t scan_state(b200_stream_t st, size_t bytes, void** out, uint32_t* epoch, bool* must_clear);
+// One line per operator call on stderr when the environment has B200_LOG=debug.
+void log_debug(const char* fmt, ...);
 // Device pointer of this device's latched error word (kernels store a status code there).
 int32_t* device_error_word(int dev);
 // Called by every operator after its launches: launch-error check + optional blocking mode.
@@ -207,35 +232,6 @@ __device__ __forceinline__ void latch_error(int32_t* word, int32_t code) {
 __device__ __forceinline__ bool error_latched(const int32_t* word) {
     return *(volatile const int32_t*)word != 0;
 }
-
-// Optional phase timing for kernel tuning (compile with -DB200_PHASE_TIMING): thread 0 of a
-// block adds the cycles spent between marks to a global table that b200_debug_phases() returns.
-#ifdef B200_PHASE_TIMING
-static __device__ unsigned long long g_phase_cycles[16];   // one table per translation unit
-#define B200_DEFINE_PHASE_READER(NAME)                                                          \
-    extern "C" int32_t NAME(unsigned long long* out16, int32_t reset) {                         \
-        cudaDeviceSynchronize();                                                                \
-        cudaMemcpyFromSymbol(out16, b200::g_phase_cycles, sizeof(unsigned long long) * 16);     \
-        if (reset) {                                                                            \
-            unsigned long long z[16] = {0};                                                     \
-            cudaMemcpyToSymbol(b200::g_phase_cycles, z, sizeof z);                              \
-        }                                                                                       \
-        return 0;                                                                               \
-    }
-#define B200_PHASE_BEGIN() long long _ph_t = clock64()
-#define B200_PHASE_MARK(i)                                                         \
-    do {                                                                           \
-        if (threadIdx.x == 0) {                                                    \
-            long long _now = clock64();                                            \
-            atomicAdd(&g_phase_cycles[i], (unsigned long long)(_now - _ph_t));     \
-            _ph_t = _now;                                                          \
-        }                                                                          \
-    } while (0)
-#else
-#define B200_DEFINE_PHASE_READER(NAME)
-#define B200_PHASE_BEGIN() do { } while (0)
-#define B200_PHASE_MARK(i) do { } while (0)
-#endif
 
 // Julia Base.max/min on floats: NaN wins, -0.0 orders below +0.0.
 template <typename F>

@@ -6,14 +6,18 @@
 namespace b200 {
 
 // ys[indices[i] - 1] = i + 1 (linear, 1-based) for every i with bools[i]; with `values` given,
-// the selected VALUES are gathered instead (xs[bools]).
+// the selected VALUES are gathered instead (xs[bools]).  A position outside 1..ny (positions that
+// are not the cumsum of this mask, or a destination that is too short) latches B200_INVALID_ARG
+// in the device's error word and skips that store, as the gather kernel below does.
 template <int BYTES>
 __global__ void __launch_bounds__(256)
-compact_kernel(void* ys, const uint8_t* bools, const int64_t* indices, const void* values, int64_t n) {
+compact_kernel(void* ys, const uint8_t* bools, const int64_t* indices, const void* values, int64_t n,
+               int64_t ny, int32_t* err_word) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         if (bools[i]) {
             const int64_t b = indices[i] - 1;
+            if (b < 0 || b >= ny) { latch_error(err_word, B200_INVALID_ARG); continue; }
             if (values == nullptr) reinterpret_cast<int64_t*>(ys)[b] = i + 1;
             else store_bits(ys, BYTES, b, load_bits(values, BYTES, i));
         }
@@ -123,11 +127,13 @@ extern "C" int32_t b200_compact(b200_stream_t st, const b200_tensor* ys, const b
     const unsigned grid = balanced_grid((n + 255) / 256, (int64_t)sm_count(st->dev) * 8);
     const uint8_t* m = reinterpret_cast<const uint8_t*>(bools->ptr);
     const int64_t* idx = reinterpret_cast<const int64_t*>(indices->ptr);
+    const int64_t ny = tensor_numel(ys);
+    int32_t* err = device_error_word(st->dev);
     switch (bytes) {
-        case 1: compact_kernel<1><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n); break;
-        case 2: compact_kernel<2><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n); break;
-        case 4: compact_kernel<4><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n); break;
-        default: compact_kernel<8><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n); break;
+        case 1: compact_kernel<1><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n, ny, err); break;
+        case 2: compact_kernel<2><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n, ny, err); break;
+        case 4: compact_kernel<4><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n, ny, err); break;
+        default: compact_kernel<8><<<grid, 256, 0, st->s>>>(ys->ptr, m, idx, vals, n, ny, err); break;
     }
     return finish(st, "b200_compact");
 }

@@ -478,14 +478,11 @@ static uint64_t identity_bits(int redop, int acc_dtype) {
 
 template <typename Tin, typename Acc>
 static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L, int64_t M, int mapop, const RedOut& out,
-                           const PeerCtx* peer = nullptr) {
+                           b200_peer_t peer = nullptr) {
     void* scr = nullptr;
     unsigned int* counters = nullptr;
     PeerCtx pc{};
-    if (peer) {
-        if (K != 1 || M != 1) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce handles full reductions only");
-        pc = *peer;
-    }
+    if (peer && (K != 1 || M != 1)) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce handles full reductions only");
     if (K == 1) {
         if (!peer && M > 1 && L <= 16) {
             const int64_t res = resident_blocks(reduce_contig_thread_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
@@ -511,6 +508,8 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
         chunk = (chunk + grain - 1) / grain * grain;
         B = (L + chunk - 1) / chunk;
         B200_TRY(scratch(st, (size_t)(M * B) * sizeof(Acc), &scr, &counters));
+        // the collective's sequence number is taken last: a call that fails above must not count
+        if (peer) B200_TRY(peer_next_context(peer, st, &pc));
         reduce_contig_block_kernel<Tin, Acc><<<balanced_grid(M * B, target), kRedThreads, 0, st->s>>>(
             (const Tin*)A, L, M, (int)B, chunk, mapop, (Acc*)scr, counters, out, pc);
         return B200_OK;
@@ -550,10 +549,37 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
 
 using namespace b200;
 
+// A rank with an empty shard still takes part in the fused all-reduce: one warp publishes the
+// operator's neutral element as this rank's partial and folds the partials of all ranks.
+template <typename Acc>
+__global__ void __launch_bounds__(32) peer_neutral_kernel(int op, RedOut out, const __grid_constant__ PeerCtx peer) {
+    switch (op) {
+        case B200_RED_ADD: block_finalize<Acc, B200_RED_ADD>(out, peer, 0, red_identity<Acc, B200_RED_ADD>()); break;
+        case B200_RED_MUL: block_finalize<Acc, B200_RED_MUL>(out, peer, 0, red_identity<Acc, B200_RED_MUL>()); break;
+        case B200_RED_MAX: block_finalize<Acc, B200_RED_MAX>(out, peer, 0, red_identity<Acc, B200_RED_MAX>()); break;
+        default: block_finalize<Acc, B200_RED_MIN>(out, peer, 0, red_identity<Acc, B200_RED_MIN>()); break;
+    }
+}
+
+static int32_t launch_peer_neutral(b200_stream_t st, b200_peer_t peer, int acc_dt, int op, const RedOut& out) {
+    PeerCtx pc{};
+    B200_TRY(peer_next_context(peer, st, &pc));
+    switch (acc_dt) {
+        case B200_F32: peer_neutral_kernel<float><<<1, 32, 0, st->s>>>(op, out, pc); break;
+        case B200_F64: peer_neutral_kernel<double><<<1, 32, 0, st->s>>>(op, out, pc); break;
+        case B200_I32: peer_neutral_kernel<int32_t><<<1, 32, 0, st->s>>>(op, out, pc); break;
+        case B200_I64: peer_neutral_kernel<int64_t><<<1, 32, 0, st->s>>>(op, out, pc); break;
+        case B200_U32: peer_neutral_kernel<uint32_t><<<1, 32, 0, st->s>>>(op, out, pc); break;
+        default: peer_neutral_kernel<uint64_t><<<1, 32, 0, st->s>>>(op, out, pc); break;
+    }
+    return B200_OK;
+}
+
 static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
                               const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
-                              int32_t ninstr, int32_t op, const void* init, const PeerCtx* peer) {
+                              int32_t ninstr, int32_t op, const void* init, b200_peer_t peer) {
     B200_TRY(enter(st));
+    StreamGuard guard(st);
     B200_TRY(check_tensor(R, "mapreduce destination"));
     if (!shape && ndim > 0) return fail(B200_INVALID_ARG, "mapreduce: null shape");
     if (ndim < 0 || ndim > B200_MAX_DIMS) return fail(B200_INVALID_ARG, "mapreduce: ndim %d outside [0,%d]", ndim, B200_MAX_DIMS);
@@ -573,12 +599,9 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
         else if (re == 1) { mask |= 1u << d; n_red *= shape[d]; }
         else return fail(B200_INVALID_ARG, "mapreduce: destination extent %lld in dim %d matches neither %lld nor 1 (check_reducedims)", (long long)re, d, (long long)shape[d]);
     }
-    if (n == 0) return B200_OK;   // empty input: R is returned untouched
+    if (n == 0 && !peer) return B200_OK;   // empty input: R is returned untouched
 
     const int acc_dt = acc_dtype_of(R->dtype);
-    Compiled C;
-    B200_TRY(compile_program(shape, ndim, leaves, nleaves, program, ninstr, acc_dt, &C));
-
     RedOut out{};
     out.R = R->ptr;
     out.rdtype = R->dtype;
@@ -588,10 +611,14 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
         memcpy(&bits, init, dtype_size(R->dtype));
         out.init = scalar_to_class(R->dtype, bits);
     }
+    Compiled C;
+    B200_TRY(compile_program(shape, ndim, leaves, nleaves, program, ninstr, acc_dt, &C));
 
     // ---- fast paths: one dense array, f in {identity, abs, abs2}
     const ProgramDesc& P = C.P;
-    bool fast = C.n_array_leaves == 1 && P.linear && tensor_is_contiguous(R) && n_red > 1;
+    // (a one-element "reduction" is a plain map and goes to the evaluator, except in the fused
+    // all-reduce, where the shard of a rank may well hold a single element)
+    bool fast = C.n_array_leaves == 1 && P.linear && tensor_is_contiguous(R) && (n_red > 1 || peer);
     int map = MAP_ID, leaf = -1, in_dt = -1;
     if (fast) {
         int pc = 0;
@@ -615,6 +642,18 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
             for (int d = i0; d <= i1; ++d) L *= shape[d];
             for (int d = i1 + 1; d < ndim; ++d) M *= shape[d];
         }
+    }
+    if (fast && n == 0) {
+        // empty shard of a sharded reduction; whether the expression is one the fused kernel
+        // handles was decided above exactly as on the ranks that hold data
+        const bool typed = (acc_dt == B200_F32 && (in_dt == B200_F32 || in_dt == B200_F16 || in_dt == B200_BF16)) ||
+                           (acc_dt == B200_F64 && in_dt == B200_F64) || (acc_dt == B200_I32 && in_dt == B200_I32) ||
+                           (acc_dt == B200_I64 && (in_dt == B200_I32 || in_dt == B200_I64));
+        if (typed) {
+            B200_TRY(launch_peer_neutral(st, peer, acc_dt, op, out));
+            return finish(st, "b200_mapreduce_allreduce");
+        }
+        fast = false;
     }
     if (fast) {
         const void* A = P.leaves[leaf].ptr;
@@ -696,11 +735,7 @@ extern "C" int32_t b200_mapreduce_allreduce(b200_peer_t peer, b200_stream_t st, 
                                             int32_t ndim, const b200_leaf* leaves, int32_t nleaves,
                                             const uint8_t* program, int32_t ninstr, int32_t op, const void* init) {
     if (!peer) return fail(B200_INVALID_ARG, "null peer group");
-    PeerCtx pc{};
-    B200_TRY(b200::peer_next_context(peer, st, &pc));
     if (R && tensor_numel(R) != 1) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce produces one element");
-    int64_t n = 1;
-    for (int d = 0; d < ndim; ++d) n *= shape ? shape[d] : 0;
-    if (n == 0) return fail(B200_UNSUPPORTED, "the fused reduce + all-reduce needs a non-empty shard on every rank");
-    return mapreduce_impl(st, R, shape, ndim, leaves, nleaves, program, ninstr, op, init, &pc);
+    // the group's sequence number advances only when a kernel that exchanges is really launched
+    return mapreduce_impl(st, R, shape, ndim, leaves, nleaves, program, ninstr, op, init, peer);
 }

@@ -16,6 +16,17 @@ namespace b200 {
 
 static thread_local std::string g_last_error;
 
+// B200_LOG: unset/empty = silent, anything = errors, "debug" = also one line per call (the
+// reference's @debug lines: src/array.jl:28, src/runtime/memory/hip.jl:58).
+static int log_level() {
+    static const int level = [] {
+        const char* lg = getenv("B200_LOG");
+        if (!lg || !lg[0]) return 0;
+        return strcmp(lg, "debug") == 0 ? 2 : 1;
+    }();
+    return level;
+}
+
 int32_t fail(int32_t code, const char* fmt, ...) {
     char buf[512];
     va_list ap;
@@ -23,10 +34,18 @@ int32_t fail(int32_t code, const char* fmt, ...) {
     vsnprintf(buf, sizeof buf, fmt, ap);
     va_end(ap);
     g_last_error = buf;
-    if (const char* lg = getenv("B200_LOG")) {
-        if (lg[0]) fprintf(stderr, "[b200] error %d: %s\n", code, buf);
-    }
+    if (log_level() >= 1) fprintf(stderr, "[b200] error %d: %s\n", code, buf);
     return code;
+}
+
+void log_debug(const char* fmt, ...) {
+    if (log_level() < 2) return;
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    fprintf(stderr, "[b200] %s\n", buf);
 }
 
 int32_t cuda_fail(cudaError_t e, const char* what) {
@@ -111,6 +130,7 @@ int sm_count(int dev) { return g_dev[dev]->sms; }
 int32_t finish(b200_stream_t st, const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, what);
+    log_debug("%s: launched on device %d, stream %p", what, st->dev, (void*)st->s);
     if (g_launch_blocking) {
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(st->s, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) return b200_stream_sync(st);
@@ -129,6 +149,7 @@ static int32_t pool_alloc(DeviceState* d, void** ptr, size_t bytes, cudaStream_t
     }
     cudaError_t e = cudaMallocFromPoolAsync(ptr, bytes, d->pool, s);
     if (e != cudaSuccess) { *ptr = nullptr; return cuda_fail(e, who); }
+    log_debug("%s: %zu bytes at %p (stream %p)", who, bytes, *ptr, (void*)s);
     std::lock_guard<std::mutex> lk(d->mu);
     d->live[*ptr] = bytes;
     d->stats.alloc_count++;
@@ -156,6 +177,7 @@ static int32_t pool_free(DeviceState* d, void* ptr, cudaStream_t s) {
 int32_t scratch(b200_stream_t st, size_t bytes, void** out, unsigned int** counters) {
     DeviceState* d;
     B200_TRY(device_state(st->dev, &d));
+    std::lock_guard<std::recursive_mutex> guard(st->mu);
     const size_t need = bytes + kCounterBytes;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     B200_CUDA(cudaStreamIsCapturing(st->s, &cap));
@@ -180,6 +202,42 @@ int32_t scratch(b200_stream_t st, size_t bytes, void** out, unsigned int** count
     if (capturing) st->scratch_in_graph = true;
     if (counters) *counters = reinterpret_cast<unsigned int*>(st->scratch);
     *out = reinterpret_cast<char*>(st->scratch) + kCounterBytes;
+    return B200_OK;
+}
+
+int32_t scan_state(b200_stream_t st, size_t bytes, void** out, uint32_t* epoch, bool* must_clear) {
+    DeviceState* d;
+    B200_TRY(device_state(st->dev, &d));
+    std::lock_guard<std::recursive_mutex> guard(st->mu);
+    const size_t need = bytes + kScanStateHeader;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    B200_CUDA(cudaStreamIsCapturing(st->s, &cap));
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
+    if (need > st->scan_state_bytes) {
+        if (capturing)
+            return fail(B200_UNSUPPORTED, "this scan needs %zu bytes of descriptor storage and the stream holds %zu: "
+                        "run it once on this stream before capturing it", need, st->scan_state_bytes);
+        size_t want = need < (size_t(1) << 20) ? (size_t(1) << 20) : need + need / 4;
+        want = (want + 255) & ~size_t(255);
+        if (st->scan_state && st->scan_state_in_graph) st->retired.push_back(st->scan_state);
+        else if (st->scan_state) B200_TRY(pool_free(d, st->scan_state, st->s));
+        st->scan_state = nullptr;
+        st->scan_state_bytes = 0;
+        st->scan_state_in_graph = false;
+        B200_TRY(pool_alloc(d, &st->scan_state, want, st->s, "scan descriptors"));
+        st->scan_state_bytes = want;
+        B200_CUDA(cudaMemsetAsync(st->scan_state, 0, want, st->s));
+        st->scan_epoch = 0;
+    }
+    if (st->scan_epoch >= (1u << 30) - 1) {      // tags wrapped: start over from clean words
+        if (capturing) return fail(B200_UNSUPPORTED, "scan descriptor tags wrapped during a capture; run the scan once outside the capture");
+        B200_CUDA(cudaMemsetAsync(st->scan_state, 0, st->scan_state_bytes, st->s));
+        st->scan_epoch = 0;
+    }
+    *epoch = ++st->scan_epoch;
+    *must_clear = capturing;
+    if (capturing) st->scan_state_in_graph = true;
+    *out = st->scan_state;
     return B200_OK;
 }
 
@@ -341,7 +399,10 @@ int32_t b200_stream_create(int32_t dev, int32_t priority, b200_stream_t* out) {
     int p = priority < 0 ? hi : (priority > 0 ? lo : (lo + hi) / 2);
     cudaStream_t s;
     B200_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, p));
-    *out = new b200_stream_s{dev, s, true, nullptr, 0, false, {}};
+    b200_stream_s* h = new b200_stream_s();
+    h->dev = dev; h->s = s; h->owned = true;
+    h->scratch = nullptr; h->scratch_bytes = 0; h->scratch_in_graph = false;
+    *out = h;
     return B200_OK;
 }
 
@@ -349,7 +410,10 @@ int32_t b200_stream_wrap(int32_t dev, void* cuda_stream, b200_stream_t* out) {
     if (!out) return fail(B200_INVALID_ARG, "null output");
     DeviceState* d;
     B200_TRY(device_state(dev, &d));
-    *out = new b200_stream_s{dev, (cudaStream_t)cuda_stream, false, nullptr, 0, false, {}};
+    b200_stream_s* h = new b200_stream_s();
+    h->dev = dev; h->s = (cudaStream_t)cuda_stream; h->owned = false;
+    h->scratch = nullptr; h->scratch_bytes = 0; h->scratch_in_graph = false;
+    *out = h;
     return B200_OK;
 }
 
@@ -358,12 +422,35 @@ int32_t b200_stream_destroy(b200_stream_t st) {
     DeviceState* d;
     B200_TRY(device_state(st->dev, &d));
     if (st->scratch) pool_free(d, st->scratch, st->s);
+    if (st->scan_state) pool_free(d, st->scan_state, st->s);
     for (void* p : st->retired) pool_free(d, p, st->s);
     if (st->owned) {
         cudaError_t e = cudaStreamDestroy(st->s);   // deferred by the runtime until work drains
         if (e != cudaSuccess) cudaGetLastError();
     }
     delete st;
+    return B200_OK;
+}
+
+// Hands the stream's operator scratch (reduction partials, radix double buffers, scan descriptors)
+// back to the pool, stream ordered; the next operator that needs scratch allocates it again.
+// Buffers whose address a captured graph holds stay.
+int32_t b200_stream_release_scratch(b200_stream_t st) {
+    if (!st) return fail(B200_INVALID_ARG, "null stream handle");
+    DeviceState* d;
+    B200_TRY(device_state(st->dev, &d));
+    std::lock_guard<std::recursive_mutex> guard(st->mu);
+    if (st->scratch && !st->scratch_in_graph) {
+        B200_TRY(pool_free(d, st->scratch, st->s));
+        st->scratch = nullptr;
+        st->scratch_bytes = 0;
+    }
+    if (st->scan_state && !st->scan_state_in_graph) {
+        B200_TRY(pool_free(d, st->scan_state, st->s));
+        st->scan_state = nullptr;
+        st->scan_state_bytes = 0;
+        st->scan_epoch = 0;
+    }
     return B200_OK;
 }
 

@@ -130,7 +130,6 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    B200_PHASE_BEGIN();
     if (tid == 0) {
         const unsigned int t = atomicAdd(a.ticket, 1u);
         if (t == a.ntiles - 1) *a.ticket = 0;
@@ -163,7 +162,6 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         }
     }
 
-    B200_PHASE_MARK(0);   // ticket, histogram clear, loads issued
     // ---- rank inside the warp: keys with equal digits get consecutive ranks in element order
     uint32_t rank[KPT];
     uint32_t* myhist = whist + warp * 256;
@@ -191,7 +189,6 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         rank[i] = base + __popc(peers & lt_mask);
     }
     __syncthreads();
-    B200_PHASE_MARK(1);   // load latency + ranking
 
     // ---- per digit: offsets of each warp inside the digit, tile count, publish
     uint32_t c = 0;
@@ -226,7 +223,6 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
     }
     __syncthreads();
 
-    B200_PHASE_MARK(2);   // digit scans, publish
     // ---- keys (and values) to their tile-local sorted position
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
@@ -236,7 +232,6 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         if (PAIRS) vexch[pos] = val[i];
     }
 
-    B200_PHASE_MARK(3);   // exchange scatter
     // ---- decoupled look-back: thread d sums digit d over all earlier tiles
     if (tid < 256) {
         uint32_t excl = 0;
@@ -284,7 +279,6 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
         s_goff[tid] = a.bin_base[tid] + excl - s_binstart[tid];
     }
     __syncthreads();
-    B200_PHASE_MARK(4);   // look-back
     if (s_abort) return;
 
     // ---- global scatter, in runs per digit
@@ -303,7 +297,6 @@ onesweep_kernel(const __grid_constant__ SweepArgs a) {
             }
         }
     }
-    B200_PHASE_MARK(5);   // global scatter issued
 }
 
 template <typename UK> struct SortCfg { static constexpr int KPT = 16; };
@@ -425,6 +418,7 @@ static int32_t key_info(int dtype, int* kind, uint64_t* expmask, int* width) {
 
 static int32_t sort_common(b200_stream_t st, const b200_tensor* x, const b200_tensor* ix, int32_t rev, const char* who) {
     B200_TRY(enter(st));
+    StreamGuard guard(st);
     B200_TRY(check_tensor(x, who));
     int64_t n = tensor_numel(x);
     int nd = 0;
@@ -466,4 +460,3 @@ extern "C" int32_t b200_sortperm(b200_stream_t st, const b200_tensor* ix, const 
     return sort_common(st, x, ix, rev, "sortperm!");
 }
 
-B200_DEFINE_PHASE_READER(b200_debug_phases_sort)

@@ -13,7 +13,7 @@ import numpy as np
 
 from ._lib import check, lib
 from .accumulate import accumulate_
-from .array import ROCArray, copyto_
+from .array import ROCArray, copyto_, with_managed
 from .broadcast import Broadcasted, materialize_
 from .runtime import Stream, current_stream
 
@@ -26,6 +26,7 @@ def _positions(bools: ROCArray, stream: Stream):
     code = bytes((0, 0, 1, 7))                      # LEAF 0, CONVERT -> Int64
     leaves = Broadcasted.leaf(flat).flatten()[1]
     t = as_int.tensor()
+    with_managed(stream, as_int, flat)
     check(lib.b200_broadcast(stream.handle, C.byref(t), leaves, 1, code, 2))
     idx = accumulate_("+", as_int, as_int, init=None, stream=stream)
     n = int(idx.view(idx.size - 1, idx.size).to_host(stream)[0]) if idx.size else 0     # blocking read, like indices[end]
@@ -39,6 +40,7 @@ def findall(bools: ROCArray, stream: Stream | None = None) -> ROCArray:
     ys = ROCArray(np.int64, (n,), stream=st)
     if n:
         ty, tb, ti = ys.tensor(), flat.tensor(), idx.tensor()
+        with_managed(st, ys, flat, idx)
         check(lib.b200_compact(st.handle, C.byref(ty), C.byref(tb), C.byref(ti), None))
     idx.unsafe_free_()
     return ys
@@ -53,6 +55,7 @@ def getindex_mask(xs: ROCArray, bools: ROCArray, stream: Stream | None = None) -
     ys = ROCArray(xs.dtype, (n,), stream=st)
     if n:
         ty, tb, ti, tv = ys.tensor(), flat.tensor(), idx.tensor(), xs.reshape(xs.size).tensor()
+        with_managed(st, ys, flat, idx, xs)
         check(lib.b200_compact(st.handle, C.byref(ty), C.byref(tb), C.byref(ti), C.byref(tv)))
     idx.unsafe_free_()
     return ys
@@ -65,9 +68,11 @@ def getindex(xs: ROCArray, ix: ROCArray, stream: Stream | None = None) -> ROCArr
     if ix.dtype not in (np.dtype(np.int64), np.dtype(np.int32)):
         raise ValueError("index vectors must be Int64 or Int32")
     st = stream or current_stream()
-    xd, ixd = xs.dense(), ix.dense()
+    xd = xs if xs.is_contiguous else xs.copy(st)
+    ixd = ix if ix.is_contiguous else ix.copy(st)
     out = ROCArray(xs.dtype, ix.dims, stream=st)
     ty, tx, ti = out.tensor(), xd.tensor(), ixd.tensor()
+    with_managed(st, out, xd, ixd)
     check(lib.b200_gather(st.handle, C.byref(ty), C.byref(tx), C.byref(ti)))
     return out
 
@@ -88,8 +93,9 @@ def _mask(x: ROCArray, dims) -> int:
 def reverse(x: ROCArray, dims=None, stream: Stream | None = None) -> ROCArray:
     """``reverse(x; dims)`` (src/kernels/reverse.jl:91-100): out of place."""
     st = stream or current_stream()
-    y = x.similar()
+    y = x.similar(stream=st)
     ty, tx = y.tensor(), x.tensor()
+    with_managed(st, y, x)
     check(lib.b200_reverse(st.handle, C.byref(ty), C.byref(tx), _mask(x, dims)))
     return y
 
@@ -97,8 +103,9 @@ def reverse(x: ROCArray, dims=None, stream: Stream | None = None) -> ROCArray:
 def reverse_(x: ROCArray, dims=None, stream: Stream | None = None) -> ROCArray:
     """``reverse!(x; dims)`` (src/kernels/reverse.jl:102-122); goes through a device copy."""
     st = stream or current_stream()
-    tmp = x.copy()
+    tmp = x.copy(st)
     tx, tt = x.tensor(), tmp.tensor()
+    with_managed(st, x, tmp)
     check(lib.b200_reverse(st.handle, C.byref(tx), C.byref(tt), _mask(x, dims)))
     tmp.unsafe_free_()
     return x

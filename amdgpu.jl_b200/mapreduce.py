@@ -17,7 +17,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import check, lib
-from .array import ROCArray
+from .array import ROCArray, with_managed
 from .broadcast import Broadcasted
 from .runtime import Stream, current_stream
 
@@ -59,13 +59,14 @@ def mapreducedim_(f, op, R: ROCArray, A, init=None, stream: Stream | None = None
         raise ValueError(f"DimensionMismatch: cannot reduce an array of size {shape} into one of size {R.dims}")
     if int(np.prod(shape, dtype=np.int64)) == 0:
         return R
-    code, leaves, nleaves, _keep = expr.flatten()
+    code, leaves, nleaves, keep = expr.flatten()
     shp = (C.c_int64 * max(1, len(shape)))(*shape)
     t = R.tensor()
     init_buf = None
     if init is not None:
         init_buf = np.asarray(init, dtype=R.dtype).tobytes()
-    check(lib.b200_mapreduce((stream or current_stream()).handle, C.byref(t), shp, len(shape), leaves, nleaves,
+    st = with_managed(stream or current_stream(), R, *keep)
+    check(lib.b200_mapreduce(st.handle, C.byref(t), shp, len(shape), leaves, nleaves,
                              code, len(code) // 2, _op_code(op), init_buf))
     return R
 
@@ -82,6 +83,7 @@ def prepared(f, op, R: ROCArray, A, init=None, stream: Stream | None = None):
     fn, ninstr, opc, nd = lib.b200_mapreduce, len(code) // 2, _op_code(op), len(shape)
 
     def launch(_keep=(keep, R, st)):
+        with_managed(st, R, *keep)
         check(fn(st.handle, C.byref(t), shp, nd, leaves, nleaves, code, ninstr, opc, init_buf))
     return launch
 

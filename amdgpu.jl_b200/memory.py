@@ -74,10 +74,17 @@ def reclaim_hook(fn) -> None:
 
 
 def reclaim(dev: int | None = None, keep: int = 0) -> None:
-    """Returns cached pool memory to the driver (``AMDGPU.reclaim``, src/memory.jl:333-344)."""
+    """Returns cached pool memory to the driver (``AMDGPU.reclaim``, src/memory.jl:333-344): the
+    registered hooks run, every open stream of the device gives up its operator scratch, then the
+    pool is trimmed to `keep` bytes."""
+    from .runtime import live_streams
+    dev = current_device() if dev is None else dev
     for fn in _reclaim_hooks:
         fn()
-    check(lib.b200_pool_trim(current_device() if dev is None else dev, keep))
+    for st in live_streams(dev):
+        st.release_scratch()
+        st.synchronize()             # the stream-ordered frees must have run before the trim
+    check(lib.b200_pool_trim(dev, keep))
 
 
 def _try_alloc(nbytes: int, stream: Stream) -> int:
@@ -141,16 +148,16 @@ class AllocCache:
     """Buffers allocated while the cache is active (``with cached(cache):``) belong to the cache:
     the arrays' finalisers and ``unsafe_free_`` leave them alone, leaving the block marks them
     free, and the next pass through the block gets the same buffers back for requests of the same
-    size on the same device.  Repeated iterations then make no allocator calls at all, which is
+    size on the same stream.  Repeated iterations then make no allocator calls at all, which is
     also what lets a block with temporaries be captured into a graph
     (test/core/graph_tests.jl:37-55)."""
 
     def __init__(self):
         self._lock = threading.Lock()
-        self.free: dict[tuple[int, int], list[int]] = {}
-        self.busy: list[tuple[tuple[int, int], int]] = []
+        self.free: dict[tuple, list[int]] = {}           # key: (device, stream, bytes)
+        self.busy: list[tuple[tuple, int]] = []
 
-    def take(self, key: tuple[int, int], alloc) -> int:
+    def take(self, key: tuple, alloc) -> int:
         with self._lock:
             pool = self.free.get(key)
             ptr = pool.pop() if pool else None
@@ -168,7 +175,7 @@ class AllocCache:
 
     def sizeof(self) -> int:
         with self._lock:
-            return builtins.sum(k[1] * len(v) for k, v in self.free.items()) + builtins.sum(k[1] for k, _ in self.busy)
+            return builtins.sum(k[-1] * len(v) for k, v in self.free.items()) + builtins.sum(k[-1] for k, _ in self.busy)
 
     def unsafe_free_(self, stream: Stream | None = None) -> None:
         """``unsafe_free!(cache)``: hand every buffer back to the pool."""

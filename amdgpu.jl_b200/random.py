@@ -13,7 +13,7 @@ import ctypes as C
 import numpy as np
 
 from ._lib import check, lib
-from .array import ROCArray
+from .array import ROCArray, with_managed
 from .runtime import Stream, current_stream
 
 UNIFORM01, UNIFORM11, NORMAL, INTEGERS, RAWBITS, NORMAL_DUP1PCT = range(6)
@@ -23,8 +23,8 @@ _M64 = np.uint64(0xFFFFFFFFFFFFFFFF)
 def fill_random_(out: ROCArray, dist: int, seed: int, stream_id: int = 0, first_index: int = 0,
                  lo: int = 0, hi: int = 0, stream: Stream | None = None) -> ROCArray:
     t = out.tensor()
-    check(lib.b200_fill_random((stream or current_stream()).handle, C.byref(t), dist, seed, stream_id,
-                               first_index, lo, hi))
+    st = with_managed(stream or current_stream(), out)
+    check(lib.b200_fill_random(st.handle, C.byref(t), dist, seed, stream_id, first_index, lo, hi))
     return out
 
 

@@ -10,10 +10,14 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
+import weakref
 from contextlib import contextmanager
 
 from . import _lib
 from ._lib import check, lib
+
+
+_live_streams: "weakref.WeakSet[Stream]" = weakref.WeakSet()
 
 
 class Stream:
@@ -28,6 +32,13 @@ class Stream:
             _handle = h
         self.handle = _handle
         self._owned = _owned
+        _live_streams.add(self)
+
+    def release_scratch(self) -> None:
+        """Returns the operator scratch this stream holds (reduction partials, radix double
+        buffers, scan descriptors) to the pool; the next operator allocates it again."""
+        if self.handle is not None:
+            check(lib.b200_stream_release_scratch(self.handle))
 
     @classmethod
     def wrap(cls, device: int, cuda_stream: int) -> "Stream":
@@ -106,6 +117,11 @@ class _TLS(threading.local):
 
 
 _tls = _TLS()
+
+
+def live_streams(device: int | None = None) -> list:
+    """The streams of this process that are still open (all devices, or one)."""
+    return [s for s in list(_live_streams) if s.handle is not None and (device is None or s.device == device)]
 
 
 def ndevices() -> int:

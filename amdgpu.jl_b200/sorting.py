@@ -24,7 +24,7 @@ import ctypes as C
 import numpy as np
 
 from ._lib import check, lib
-from .array import ROCArray, copyto_
+from .array import ROCArray, copyto_, with_managed
 from .runtime import Stream, current_stream
 
 _LT_REVERSED = {None: False, "isless": False, "<": False, ">": True, "!isless": True}
@@ -38,15 +38,15 @@ def _order(rev: bool, lt) -> bool:
     return bool(rev) != _LT_REVERSED[lt]
 
 
-def _keys(x: ROCArray, by) -> ROCArray:
+def _keys(x: ROCArray, by, stream: Stream) -> ROCArray:
     """``by.(x)`` as a dense device vector (`x` itself when `by` is the identity)."""
     if by is None:
-        return x.dense()
+        return x if x.is_contiguous else x.copy(stream)
     from .broadcast import Broadcasted
     expr = by(x.dot)
     if not isinstance(expr, Broadcasted):
         raise ValueError("`by` must map the lazy operand to a broadcast expression (e.g. lambda k: 2 * k)")
-    return expr.materialize()
+    return expr.materialize(stream)
 
 
 def _gather(x: ROCArray, ix: ROCArray, stream: Stream | None = None) -> ROCArray:
@@ -61,10 +61,11 @@ def sort_(x: ROCArray, rev: bool = False, lt=None, by=None, stream: Stream | Non
     rev = _order(rev, lt)
     st = stream or current_stream()
     if by is not None:
-        perm = sortperm_(ROCArray(np.int64, x.dims), x, rev=rev, by=by, stream=st)
-        return copyto_(x, _gather(x.dense(), perm, st), st)
-    xd = x.dense()
+        perm = sortperm_(ROCArray(np.int64, x.dims, stream=st), x, rev=rev, by=by, stream=st)
+        return copyto_(x, _gather(x if x.is_contiguous else x.copy(st), perm, st), st)
+    xd = x if x.is_contiguous else x.copy(st)
     t = xd.tensor()
+    with_managed(st, xd)
     check(lib.b200_sort(st.handle, C.byref(t), 1 if rev else 0))
     if xd is not x:
         copyto_(x, xd, st)
@@ -85,9 +86,11 @@ def sortperm_(ix: ROCArray, x: ROCArray, rev: bool = False, lt=None, by=None, st
     if not ix.is_contiguous:
         raise ValueError("sortperm!: the index vector must be dense")
     rev = _order(rev, lt)
-    keys = _keys(x, by)
+    st = stream or current_stream()
+    keys = _keys(x, by, st)
     ti, tx = ix.tensor(), keys.tensor()
-    check(lib.b200_sortperm((stream or current_stream()).handle, C.byref(ti), C.byref(tx), 1 if rev else 0))
+    with_managed(st, ix, keys)
+    check(lib.b200_sortperm(st.handle, C.byref(ti), C.byref(tx), 1 if rev else 0))
     return ix
 
 

@@ -4,12 +4,13 @@
 A step is one pass of the sharded workload over one batch of synthetic input: every GPU holds a
 contiguous shard of 2^30 Float32 elements of x, y, z (U[-1,1), counter-based generator, seed 4)
 and runs  r .= x .* y .+ exp.(-abs.(z))  followed by  sum(abs2, r)  whose one-element partial is
-all-reduced over NCCL on the same stream.  With 8 GPUs that is the 2^33-element configuration;
-per-GPU work is fixed as N grows (weak scaling).  The metric is achieved HBM bandwidth in GB/s:
-algorithmic bytes (16 B/element for the broadcast + 4 B/element for the reduction) over the
-device time of the step, maximum over ranks.
+all-reduced inside the reduction kernel.  With 8 GPUs that is the 2^33-element configuration;
+per-GPU work is fixed as N grows (weak scaling; --scaling strong splits 2^33 over the GPUs
+instead).  The metric is achieved HBM bandwidth in GB/s: algorithmic bytes (16 B/element for the
+broadcast + 4 B/element for the reduction) over the device time of the step, maximum over ranks.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-suite]
+                    [--scaling weak|strong] [--collective fused|nccl|none] [--transport host|vmm|ipc]
 
 For N > 1 launch through torchrun (one rank per GPU); rank 0 prints ONE JSON line.
 """
@@ -322,13 +323,25 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
     return out
 
 
-def cpu_reference_step(n_sample: int, steps: int, warmup: int):
-    """The CPU arm: the same step (fused broadcast, then sum of squares) by the C restatement of
-    Base's loops on all host threads, over a bounded sample of the shard."""
-    orc = entry.load_oracle()
+METRIC = "achieved HBM GB/s (algorithmic bytes / time), fused broadcast + sum(abs2) with allreduce"
+CPU_SAMPLE_LOG2 = 26
+
+
+def host_threads() -> int:
+    """Threads this process may run on.  (torchrun exports OMP_NUM_THREADS=1, so the OpenMP default
+    is not the number to use; the count is passed to every parallel region explicitly.)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_reference_step(n_sample: int, steps: int, warmup: int, threads: int) -> float:
+    """Seconds per step of the CPU arm: the same step (fused broadcast, then sum of squares) by the
+    C restatement of Base's loops on `threads` host threads, over a bounded sample of the shard."""
+    entry.load_oracle()
     from b200_oracle import c_oracle as co   # noqa: E402
     lib = co.load()
-    threads = lib.ora_max_threads()
     rng = np.random.default_rng(4)
     x, y, z = (rng.random(n_sample, dtype=np.float32) * 2 - 1 for _ in range(3))
     r = np.empty_like(x)
@@ -342,8 +355,87 @@ def cpu_reference_step(n_sample: int, steps: int, warmup: int):
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
-    dt = (time.perf_counter() - t0) / steps
-    return dt, threads
+    return (time.perf_counter() - t0) / steps
+
+
+def numpy_reference_step(n_sample: int, steps: int) -> float:
+    """Second yardstick: the same step written with NumPy array expressions (temporaries and all)."""
+    rng = np.random.default_rng(4)
+    x, y, z = (rng.random(n_sample, dtype=np.float32) * 2 - 1 for _ in range(3))
+    def step():
+        r = x * y + np.exp(-np.abs(z))
+        return float(np.sum(r * r, dtype=np.float32))
+    step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    return (time.perf_counter() - t0) / steps
+
+
+def cpu_baseline(steps: int, warmup: int) -> dict:
+    """The CPU numbers that stand beside the GPU line: all host threads (the `value`), one thread,
+    and NumPy; one protocol wherever it is reported."""
+    n_sample = 1 << CPU_SAMPLE_LOG2
+    threads = host_threads()
+    gbs = lambda dt: round(BYTES_PER_ELEM * n_sample / dt / 1e9, 3)
+    dt_all = cpu_reference_step(n_sample, steps, warmup, threads)
+    dt_one = cpu_reference_step(n_sample, max(1, min(steps, 5)), 1, 1)
+    dt_np = numpy_reference_step(n_sample, max(1, min(steps, 3)))
+    return {"value": gbs(dt_all), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"2^{CPU_SAMPLE_LOG2}-element slice of the shard per step, {steps} steps after {warmup} warm-ups; "
+                      "Julia Base cannot run on this box, this is its C restatement (oracle/base_oracle.c, OpenMP)",
+            "all_threads": {"value": gbs(dt_all), "threads": threads, "ms_per_step": round(dt_all * 1e3, 3)},
+            "single_thread": {"value": gbs(dt_one), "threads": 1, "ms_per_step": round(dt_one * 1e3, 3)},
+            "numpy": {"value": gbs(dt_np), "threads": "numpy default", "ms_per_step": round(dt_np * 1e3, 3)},
+            "julia_base": "unavailable on this box"}
+
+
+def sharded_scan_record(pkg, dist, rank, world, local_rank, st, log2_elems: int = 27) -> dict:
+    """Sharded inclusive scan of Int32 (the exclusive prefix of the per-shard totals seeds every
+    rank's local scan): timed with events, checked exactly.  Every rank regenerates its own shard on
+    the host, the shard totals travel over the host channel, so each rank knows the value its last
+    element must have and can compare a stretch of its output bit for bit."""
+    R = pkg.random
+    n = 1 << log2_elems
+    first = rank * n
+    shard = R.fill_random_(pkg.ROCArray(np.int32, n), R.INTEGERS, seed=2, first_index=first, lo=-100, hi=100)
+    out = pkg.ROCArray(np.int32, n)
+    comm = None
+    if world > 1:
+        comm = pkg.sharded.init_comm(rank, world, local_rank, dist.exchange)
+    ops = pkg.sharded.ShardedOps(pkg.sharded.DeviceBackend(comm, world, stream=st), rank, world)
+    try:
+        ops.accumulate("+", out, shard, timeout=60.0 if world > 1 else None)
+        st.synchronize()
+        dist.barrier()
+        reps = 5
+        a, b = pkg.Event(timing=True), pkg.Event(timing=True)
+        a.record(st)
+        for _ in range(reps):
+            ops.accumulate("+", out, shard)
+        b.record(st)
+        b.synchronize()
+        ms = dist.max(pkg.elapsed_ms(a, b) / reps)
+        # the check: host totals of every shard -> the carry of this rank -> exact comparison
+        host = np.empty(n, dtype=np.int32)
+        blk = 1 << 22
+        for s in range(0, n, blk):
+            host[s:s + blk] = R.host_integers(2, 0, first + s, blk, -100, 100)
+        totals = dist.allgather(int(host.sum(dtype=np.int64)))
+        carry = sum(totals[:rank])
+        wrap = lambda v: np.int64(v).astype(np.int32)
+        last = int(out.view(n - 1, n).to_host()[0])
+        head = out.view(0, 1 << 20).to_host()
+        want_head = (np.cumsum(host[:1 << 20], dtype=np.int64) + carry).astype(np.int32)
+        ok = last == int(wrap(carry + totals[rank])) and np.array_equal(head, want_head)
+        exact = all(dist.allgather(bool(ok)))
+    finally:
+        pkg.device_synchronize()
+        dist.barrier()
+        if comm is not None:
+            pkg.sharded.destroy_comm(comm)
+    return {"elements_per_gpu": n, "dtype": "Int32", "ms": round(ms, 4), "GB/s": round(8 * n * world / ms / 1e6, 1),
+            "exact": bool(exact), "method": "local totals -> all-gather of one element per rank -> carry folded on the device -> seeded local scan"}
 
 
 def main():
@@ -354,35 +446,42 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-suite", action="store_true", help="skip the per-configuration kernel numbers")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl", "none"],
-                    help="fused: reduction and all-reduce in one kernel over NVLink peer memory; nccl: reduction kernel, then "
-                         "ncclAllReduce on the same stream; none: diagnostic, ranks run their shards without any exchange")
+                    help="fused: reduction and all-reduce in one kernel over exchange slots all ranks can write; nccl: reduction "
+                         "kernel, then ncclAllReduce on the same stream; none: diagnostic, ranks run their shards without any exchange")
+    ap.add_argument("--transport", default=None, choices=["host", "vmm", "ipc"],
+                    help="where the fused exchange keeps its slots (default: B200_PEER_TRANSPORT or the library default)")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: 2^LOG2_ELEMS elements per GPU at every N; strong: 2^33 elements in total, split over the GPUs "
+                         "(at N=1: 2^33 when at least 140 GiB are free, else 2^32)")
     ap.add_argument("--case", default=None, help="run only the suite cases whose name starts with this (e.g. c3_scan) and print them")
     ap.add_argument("--shrink", type=int, default=0, help="with --case: divide the sizes by 2^SHRINK (small cases for profiler captures)")
     ap.add_argument("--reps-scale", type=float, default=1.0, help="with --case: scale the repetition counts")
     ap.add_argument("--log2-elems", type=int, default=int(os.environ.get("B200_BENCH_LOG2_ELEMS", "30")),
-                    help="log2 of the elements per GPU (30 = the 2^33 / 8-GPU configuration)")
+                    help="log2 of the elements per GPU in weak mode (30 = the 2^33 / 8-GPU configuration)")
     args = ap.parse_args()
     rank, world, local_rank = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")))
     warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    n = 1 << args.log2_elems
-    workload = (f"config5 shard: r .= x.*y .+ exp.(-abs.(z)); sum(abs2, r) all-reduced over the ranks (--collective fused: inside the reduction kernel over NVLink peer memory; nccl: separate NCCL call); 2^{args.log2_elems} Float32 "
-                f"elements per GPU (2^33 total at 8 GPUs)")
+
+    def workload_text(log2_per_gpu, total_log2):
+        return (f"config5: r .= x.*y .+ exp.(-abs.(z)); sum(abs2, r) all-reduced over the ranks; Float32, U[-1,1), "
+                f"2^{log2_per_gpu} elements per GPU, 2^{total_log2} in total ({args.scaling} scaling; the stated "
+                f"configuration is 2^33 in total)")
 
     if args.impl == "reference":
         if rank != 0:
             return
-        n_sample = 1 << 26
-        dt, threads = cpu_reference_step(n_sample, max(1, args.steps), args.warmup)
-        val = BYTES_PER_ELEM * n_sample / dt / 1e9
-        line = {"impl": "reference", "metric": "achieved HBM GB/s (algorithmic bytes / time), fused broadcast + sum(abs2)",
-                "value": round(val, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        steps = max(1, args.steps)
+        cpu = cpu_baseline(steps, args.warmup)
+        val = cpu["value"]
+        lg = args.log2_elems
+        line = {"impl": "reference", "metric": METRIC,
+                "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": cpu["all_threads"]["ms_per_step"], "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
-                "config": {"workload": workload, "sample": f"2^26 elements per step on the host ({threads} threads)"},
-                "cpu_baseline": {"value": round(val, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-                                 "sample": "2^26-element slice of the shard per step; Julia Base cannot run here, "
-                                           "this is its C restatement with OpenMP over all host threads"},
-                "e2e": {"value": round(val, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+                "config": {"workload": workload_text(lg, lg + max(0, (world - 1).bit_length())),
+                           "sample": f"2^{CPU_SAMPLE_LOG2} elements per step on the host ({cpu['cores']} threads)"},
+                "cpu_baseline": cpu,
+                "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
         return
 
@@ -397,9 +496,23 @@ def main():
     dist = Dist(rank, world)
     pkg.device_(local_rank)
     st = pkg.current_stream()
+    if args.scaling == "strong":
+        total_log2 = 33
+        if world == 1 and pkg.mem_info()[0] < (140 << 30):
+            total_log2 = 32
+        n = (1 << total_log2) // world
+    else:
+        n = 1 << args.log2_elems
+        total_log2 = args.log2_elems + (world - 1).bit_length()
+    log2_per_gpu = n.bit_length() - 1
+    workload = workload_text(log2_per_gpu, total_log2)
     comm = peer = None
-    if world > 1 and args.collective == "fused":
-        peer = pkg.sharded.init_peer(rank, world, local_rank, dist.allgather)
+    transport = None
+    if args.collective == "fused":       # every N runs the same entry point, a group of one rank included
+        peer = pkg.sharded.init_peer(rank, world, local_rank, dist.allgather, transport=args.transport)
+        tr, sq = C.c_int32(), C.c_uint64()
+        pkg._lib.check(pkg._lib.lib.b200_peer_info(peer, C.byref(tr), C.byref(sq)))
+        transport = ("host", "vmm", "ipc")[tr.value]
     elif world > 1 and args.collective == "nccl":
         comm = pkg.sharded.init_comm(rank, world, local_rank, dist.exchange)
     R, bc = pkg.random, pkg.broadcast
@@ -411,9 +524,10 @@ def main():
     expr = x.dot * y.dot + bc.exp(-bc.abs_(z))
     launches = [0]
     fused_step = pkg.sharded.prepared_mapreduce_allreduce(peer, bc.abs2(r), "+", part, zero, st) if peer is not None else None
+    bc_step = bc.prepared(r, expr, st)
 
     def step():
-        pkg.materialize_(r, expr)
+        bc_step()
         launches[0] += 2
         if fused_step is not None:
             fused_step()                       # sum(abs2, r) and the all-reduce, one kernel
@@ -449,13 +563,34 @@ def main():
 
     # ---- kernel-level roofline: the broadcast kernel moves 16 of the 20 bytes per element
     peak, peak_kind = measured_peak()
-    ms_bc = time_loop(pkg, st, lambda: pkg.materialize_(r, expr), 10)
+    ms_bc = time_loop(pkg, st, bc_step, 10)
     ms_red = time_loop(pkg, st, lambda: pkg.mapreducedim_("abs2", "+", part, r, init=zero), 10)
     ach = 16 * n / ms_bc / 1e6
     ms_coll = None
     if fused_step is not None:
         dist.barrier()
-        ms_coll = dist.max(time_loop(pkg, st, fused_step, 10))     # reduction + all-reduce in one kernel
+        ms_coll = time_loop(pkg, st, fused_step, 10)     # reduction + all-reduce in one kernel
+    per_rank = dist.allgather({"bc": ms_bc, "red": ms_red, "coll": ms_coll})
+    spread = lambda k: None if per_rank[0][k] is None else {"min": round(min(p[k] for p in per_rank), 4), "max": round(max(p[k] for p in per_rank), 4)}
+
+    # ---- checks that travel with the number.  (1) a stretch of rank 0's shard against a Float64
+    # sum computed on the host from regenerated inputs; (2) the all-reduced value against the sum
+    # of the ranks' own local reductions
+    nc = min(n, 1 << 24)
+    chk = pkg.ROCArray(np.float32, 1)
+    pkg.mapreducedim_("abs2", "+", chk, r.view(0, nc), init=zero)
+    gpu_sub = float(chk.to_host()[0])
+    pkg.mapreducedim_("abs2", "+", chk, r, init=zero)
+    locals_ = dist.allgather(float(chk.to_host()[0]))
+    check = {"allreduce_vs_sum_of_local_reductions": abs(total_sq - sum(locals_)) <= 1e-5 * abs(sum(locals_))}
+    if rank == 0:
+        blk, host_sub = 1 << 22, 0.0
+        for s in range(0, nc, blk):
+            hx, hy, hz = (R.host_uniform11(4, k, first + s, min(blk, nc - s)).astype(np.float64) for k in range(3))
+            hr = (hx.astype(np.float32) * hy.astype(np.float32)).astype(np.float64) + np.exp(-np.abs(hz))
+            host_sub += float((hr * hr).sum())
+        check.update({"sub_shard_elements": nc, "gpu_sum_abs2": gpu_sub, "host_float64_sum_abs2": host_sub,
+                      "sub_shard_rel_err": abs(gpu_sub - host_sub) / host_sub, "sub_shard_ok": abs(gpu_sub - host_sub) <= 1e-5 * host_sub})
 
     # ---- end to end through the public API with host buffers
     ne = min(n, 1 << 28)
@@ -499,16 +634,6 @@ def main():
         L.b200_host_free(p)
     L.b200_host_free(hres)
 
-    suite = None
-    cpu = None
-    if rank == 0 and world == 1:
-        dt, threads = cpu_reference_step(1 << 26, 5, 1)
-        cpu = {"value": round(BYTES_PER_ELEM * (1 << 26) / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-               "sample": "2^26-element slice of the shard, 5 steps; C restatement of Base's loops with OpenMP on all host threads "
-                         "(Julia Base itself cannot run on this box)"}
-        if not args.no_suite:
-            del x, y, z, r, xe, ye, ze, re_, expr, expr_e
-            suite = run_suite(pkg, peak)
     dist.barrier()
     if comm is not None:
         pkg.sharded.destroy_comm(comm)
@@ -516,27 +641,42 @@ def main():
         pkg.device_synchronize()
         dist.barrier()
         pkg.sharded.destroy_peer(peer)
+    del x, y, z, r, xe, ye, ze, re_, expr, expr_e, bc_step, fused_step, fused_e
+    # ---- the sharded scan (after every timed region: it brings up an NCCL communicator)
+    scan = sharded_scan_record(pkg, dist, rank, world, local_rank, st)
+
+    suite = None
+    cpu = None
+    if rank == 0 and world == 1:
+        cpu = cpu_baseline(max(1, min(args.steps, 20)), max(1, min(args.warmup, 5)))
+        if not args.no_suite and args.scaling == "weak":
+            suite = run_suite(pkg, peak)
+    dist.barrier()
     dist.close()
     if rank != 0:
         return
     line = {
-        "metric": "achieved HBM GB/s (algorithmic bytes / time), fused broadcast + sum(abs2) with allreduce",
+        "metric": METRIC,
         "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
-        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload, "elements_per_gpu": n, "l2": "inputs (12 GiB per GPU) are far larger than L2",
-                   "frac_of_8TBs_per_gpu": round(value / world / NOMINAL_HBM_GBS, 3), "check_sum_abs2": total_sq,
-                   "collective": args.collective if world > 1 else "none"},
+        "config": {"workload": workload, "elements_per_gpu": n, "l2": f"inputs ({12 * n >> 30} GiB per GPU) are far larger than L2",
+                   "frac_of_8TBs_per_gpu": round(value / world / NOMINAL_HBM_GBS, 3), "check_sum_abs2": total_sq, "check": check,
+                   "collective": args.collective, "transport": transport, "sharded_scan": scan},
         "roofline": {"bound": "hbm", "kernel": "ew_stream_kernel<float, MulAddExpNegAbsF> (r .= x.*y .+ exp.(-abs.(z)))",
                      "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 3),
                      "peak_source": f"{peak_kind} copy bandwidth", "traffic": round(EW_TRAFFIC_BYTES_PER_ELEM * n),
-                     "traffic_source": "ncu capture at 2^26 elements scaled by the element count",
-                     "ms_per_launch": round(ms_bc, 4), "algorithmic_bytes_per_launch": 16 * n,
+                     "traffic_source": "ncu capture at 2^26 elements scaled by the element count (in that capture 3 % of the "
+                                       "output was still dirty in L2 when the kernel ended, so the figure is a little below "
+                                       "the 16 B per element a full-size launch moves)",
+                     "ms_per_launch": round(ms_bc, 4), "ms_per_launch_over_ranks": spread("bc"), "algorithmic_bytes_per_launch": 16 * n,
                      "reduce_kernel": {"ms_per_launch": round(ms_red, 4), "achieved": round(4 * n / ms_red / 1e6, 1),
-                                       "frac": round(4 * n / ms_red / 1e6 / peak, 3)},
-                     "fused_reduce_allreduce_ms": None if ms_coll is None else round(ms_coll, 4)},
+                                       "frac": round(4 * n / ms_red / 1e6 / peak, 3), "ms_per_launch_over_ranks": spread("red")},
+                     "fused_reduce_allreduce_ms": None if ms_coll is None else round(ms_coll, 4),
+                     "fused_reduce_allreduce_ms_over_ranks": spread("coll")},
         "e2e": {"value": round(e2e_val, 2), "unit": "GB/s", "h2d_bytes_per_step": 12 * ne, "d2h_bytes_per_step": 4,
-                "elements_per_gpu": ne, "ms_per_step": round(e2e_ms, 3)},
+                "elements_per_gpu": ne, "ms_per_step": round(e2e_ms, 3),
+                "note": "PCIe-bound: 12 B per element cross the link for 20 B of metric"},
         "gpu_launches": timed_launches,
         "clocks": clocks,
     }

@@ -147,6 +147,10 @@ int32_t b200_stream_destroy(b200_stream_t st);
 int32_t b200_stream_sync(b200_stream_t st);
 /* replaces HIP.isdone(stream) (src/hip/stream.jl:45-55): B200_OK or B200_NOT_READY */
 int32_t b200_stream_query(b200_stream_t st);
+/* Returns the stream's operator scratch (block partials, radix double buffers, scan descriptors)
+ * to the pool, stream ordered; part of reclaim (src/memory.jl:333-344).  Scratch whose address a
+ * captured graph holds is kept. */
+int32_t b200_stream_release_scratch(b200_stream_t st);
 int32_t b200_stream_device(b200_stream_t st, int32_t* dev);
 int32_t b200_stream_raw(b200_stream_t st, void** cuda_stream);
 /* replaces HIPEvent (src/hip/event.jl:1-75) */
@@ -296,6 +300,15 @@ int32_t b200_comm_unique_id(uint8_t id_out[128]);
 int32_t b200_comm_init_rank(b200_comm_t* out, int32_t nranks, int32_t rank,
                             const uint8_t id[128], int32_t dev);
 int32_t b200_comm_destroy(b200_comm_t comm);
+/* Host-side failure detection for the collectives: waits until `st` has drained (st == NULL: looks
+ * at the communicator only, once the time is up B200_NOT_READY while NCCL still reports progress),
+ * polling ncclCommGetAsyncError meanwhile; an asynchronous error, or `timeout_ms` passing with the
+ * stream still busy (a rank that never arrived), aborts the communicator (ncclCommAbort) and
+ * returns B200_NCCL_ERROR - after that the communicator only accepts b200_comm_destroy.  Closest
+ * relative in the reference: the watchdog on a stream that does not finish, src/hip/stream.jl:99-126.
+ * Environment B200_NCCL_LIB names the NCCL library to load instead of libnccl.so.2;
+ * b200_comm_init_rank with dev < 0 creates a communicator that is not bound to a device. */
+int32_t b200_comm_check(b200_comm_t comm, b200_stream_t st, int32_t timeout_ms);
 /* in-place all-reduce of `count` elements of R's dtype on the stream, directly after the kernel
  * that produced them (no host round trip) */
 int32_t b200_allreduce(b200_comm_t comm, void* buf, size_t count, int32_t dtype, int32_t op,
@@ -310,18 +323,39 @@ int32_t b200_allgather(b200_comm_t comm, const void* send, void* recv, size_t co
  * B200_LOOKBACK_TIMEOUT, which the next b200_stream_sync returns.  No fault, no unbounded spin. */
 int32_t b200_selftest_wait_timeout(b200_stream_t st, uint32_t polls);
 
-/* Fused reduce + all-reduce over NVLink peer memory (no counterpart in the reference, which has
- * no collective layer).  Every rank calls b200_peer_create, the 64-byte handles are gathered on
- * the host (rank r's handle at handles[64*r]), every rank calls b200_peer_connect.  All ranks
- * must then issue the same sequence of b200_mapreduce_allreduce calls. */
-int32_t b200_peer_create(int32_t dev, int32_t rank, int32_t nranks, b200_peer_t* out, uint8_t handle_out[64]);
+/* Fused reduce + all-reduce over exchange slots that every rank of a group can write (no
+ * counterpart in the reference, which has no collective layer).  Every rank calls b200_peer_create,
+ * the 64-byte handles are gathered on the host (rank r's handle at handles[64*r]), every rank calls
+ * b200_peer_connect.  All ranks must then issue the same sequence of b200_mapreduce_allreduce calls.
+ * `transport` says where the slots live:
+ *   B200_PEER_HOST  POSIX shared memory registered with the CUDA runtime in every rank; stores and
+ *                   polls cross PCIe; no GPU maps another GPU's memory (the handle is the name);
+ *   B200_PEER_VMM   one 2 MiB device allocation per rank, exported as a file descriptor and mapped
+ *                   by the peers over NVLink - peer access for that allocation only.  The handle
+ *                   holds {pid, fd}; a descriptor is only valid inside its process, so either the
+ *                   host code passes it over a Unix socket (SCM_RIGHTS) and rewrites pid/fd before
+ *                   b200_peer_connect, or the library fetches it with pidfd_getfd (needs the right
+ *                   to inspect the exporting process);
+ *   B200_PEER_IPC   cudaMalloc + CUDA IPC handle; opening it enables peer access device wide.
+ * A group of one rank needs no connect. */
+enum { B200_PEER_HOST = 0, B200_PEER_VMM = 1, B200_PEER_IPC = 2 };
+int32_t b200_peer_create(int32_t dev, int32_t rank, int32_t nranks, int32_t transport, b200_peer_t* out,
+                         uint8_t handle_out[64]);
 int32_t b200_peer_connect(b200_peer_t peer, const uint8_t* handles);
+/* how often the exchange polls for a peer's partial before it gives up and latches
+ * B200_LOOKBACK_TIMEOUT (default 2^26, about ten seconds with the back-off) */
+int32_t b200_peer_set_poll_budget(b200_peer_t peer, uint32_t polls);
+/* transport of the group and the number of collectives issued so far (either may be NULL) */
+int32_t b200_peer_info(b200_peer_t peer, int32_t* transport, uint64_t* seq);
 int32_t b200_peer_destroy(b200_peer_t peer);
 /* mapreducedim! to ONE element followed by an all-reduce of that element over the peer group,
  * in a single kernel: the block that completes the local reduction stores the partial into every
  * rank's exchange slot and folds all ranks' partials in rank order (identical bits on all ranks).
  * Restricted to a full reduction of one dense array with f in {identity, abs, abs2}; other
- * cases return B200_UNSUPPORTED (use b200_mapreduce + b200_allreduce).  Waits are bounded. */
+ * cases return B200_UNSUPPORTED before anything is exchanged (use b200_mapreduce +
+ * b200_allreduce) - that verdict depends on the expression and element types only, so all ranks
+ * reach it together.  A rank whose shard is empty takes part with the operator's neutral element.
+ * Waits are bounded. */
 int32_t b200_mapreduce_allreduce(b200_peer_t peer, b200_stream_t st, const b200_tensor* R,
                                  const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
                                  int32_t nleaves, const uint8_t* program, int32_t ninstr, int32_t op,

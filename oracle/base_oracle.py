@@ -137,11 +137,21 @@ _MAPS = {
 def _fold(op, x, axis):
     if op in ("+", "add"): return np.add.reduce(x, axis=axis, keepdims=True)
     if op in ("*", "mul"): return np.multiply.reduce(x, axis=axis, keepdims=True)
-    if op == "max":
-        r = np.max(x, axis=axis, keepdims=True)     # NaN-propagating like Base.max
-        return r
-    if op == "min": return np.min(x, axis=axis, keepdims=True)
-    raise ValueError(op)
+    if op not in ("max", "min"):
+        raise ValueError(op)
+    # Base.max / Base.min (base/math.jl): NaN wins, and -0.0 orders below +0.0.  NumPy's max/min
+    # propagate NaN as well but leave the sign of a zero result open, so it is fixed here: a zero
+    # maximum is +0.0 as soon as one +0.0 takes part, a zero minimum is -0.0 as soon as one -0.0 does.
+    r = (np.max if op == "max" else np.min)(x, axis=axis, keepdims=True)
+    if _is_float(np.asarray(x).dtype):
+        x = np.asarray(x)
+        if op == "max":
+            has = np.any((x == 0) & ~np.signbit(x), axis=axis, keepdims=True)
+            r = np.where(r == 0, np.where(has, x.dtype.type(0.0), x.dtype.type(-0.0)), r)
+        else:
+            has = np.any((x == 0) & np.signbit(x), axis=axis, keepdims=True)
+            r = np.where(r == 0, np.where(has, x.dtype.type(-0.0), x.dtype.type(0.0)), r)
+    return r
 
 
 def _op2(op, a, b):

@@ -154,3 +154,47 @@ def test_scans_down_a_strided_dimension(gpu, orc, sizes):
     src = gpu.ROCArray.from_host(rng.random(sizes).astype(np.float32))
     gpu.accumulate_("+", dst, src, dims=2)
     assert_close(dst.to_host(), orc.accumulate("+", src.to_host(), axis=1), 1e-5)
+
+
+def test_ring_kernel_variants(gpu, orc):
+    """The one-pass kernel for long dense vectors: in place, exclusive, seeded, max/min/prod, 16-bit
+    elements, a last tile of every fill level, many launches in a row (descriptor tags, alternating
+    ticket words) and a captured launch that is replayed."""
+    rng = np.random.default_rng(9)
+    tile = 8192                                   # Float32 elements per tile of the ring kernel
+    for n in (1 << 18, (1 << 18) + 4, 5 * tile - 4, 148 * tile, 149 * tile + 2044, 3 * 148 * tile + 12, (1 << 24) + 8):
+        x = rng.integers(-100, 101, n).astype(np.int32)
+        xd = gpu.ROCArray.from_host(x)
+        ref = np.cumsum(x, dtype=np.int32)
+        assert np.array_equal(gpu.cumsum(xd).to_host(), ref), n
+        ex = gpu.accumulate_("+", gpu.ROCArray(np.int32, n), xd, init=np.int32(-9), inclusive=False).to_host()
+        assert ex[0] == -9 and np.array_equal(ex[1:], (ref[:-1] - 9).astype(np.int32)), n
+        assert gpu.accumulate_("+", xd, xd, init=None) is xd            # in place
+        assert np.array_equal(xd.to_host(), ref), n
+    n = (1 << 21) + 16
+    w = rng.standard_normal(n).astype(np.float32)
+    wd = gpu.ROCArray.from_host(w)
+    assert np.array_equal(gpu.accumulate("max", wd, init=None).to_host(), np.maximum.accumulate(w))
+    assert np.array_equal(gpu.accumulate("min", wd, init=np.float32(0.5)).to_host(), np.minimum.accumulate(np.minimum(w, 0.5)))
+    g = (1.0 + 1e-6 * rng.standard_normal(n)).astype(np.float32)
+    assert_close(gpu.cumprod(gpu.ROCArray.from_host(g)).to_host(), np.cumprod(g.astype(np.float64)), 1e-4)
+    f = rng.random(n).astype(np.float32)
+    assert_close(gpu.cumsum(gpu.ROCArray.from_host(f)).to_host(), np.cumsum(f.astype(np.float64)), 1e-5)
+    h = np.where(np.arange(n) % 2 == 0, 1.0, -1.0).astype(np.float16)
+    assert np.array_equal(gpu.cumsum(gpu.ROCArray.from_host(h)).to_host(), (np.arange(n) % 2 == 0).astype(np.float16))
+    u = rng.integers(0, 1 << 31, n).astype(np.uint32)
+    assert np.array_equal(gpu.cumsum(gpu.ROCArray.from_host(u)).to_host(), np.cumsum(u, dtype=np.uint32))
+    # many launches back to back, then a captured launch replayed between ordinary ones
+    x = rng.integers(-100, 101, 1 << 20).astype(np.int32)
+    xd, out = gpu.ROCArray.from_host(x), gpu.ROCArray(np.int32, 1 << 20)
+    ref = np.cumsum(x, dtype=np.int32)
+    for _ in range(40):
+        gpu.accumulate_("+", out, xd, init=None)
+    assert np.array_equal(out.to_host(), ref)
+    graph = gpu.captured(lambda: gpu.accumulate_("+", out, xd, init=None))
+    for k in range(4):
+        out.fill_(0)
+        gpu.launch(graph)
+        assert np.array_equal(out.to_host(), ref), k
+        gpu.accumulate_("+", out, xd, init=np.int32(k))                   # ordinary launches in between
+        assert np.array_equal(out.to_host(), (ref + k).astype(np.int32)), k

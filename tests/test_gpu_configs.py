@@ -111,3 +111,29 @@ def test_config5_shard_2p30(gpu, orc):
         c = r.view(s, s + chunk).to_host().astype(np.float64)
         ref_total += float((c * c).sum())
     assert_close(total, ref_total, 1e-5)
+
+
+def test_more_than_2p32_elements_on_one_gpu(gpu, orc):
+    """Config 5 on a single GPU holds 2^33 elements per array; here broadcast and reduction run
+    over 2^32 + 5 Float32 elements (index arithmetic beyond 32 bits, ragged tail).  Checked at the
+    2^32 boundary and at the tail against the host, and through linearity: the sum over the whole
+    array equals the sum of the sums over two parts that each stay below 2^32 elements."""
+    R, n = gpu.random, (1 << 32) + 5
+    free, _ = gpu.mem_info()
+    if free < 40 << 30:
+        pytest.skip("needs 40 GiB of free device memory")
+    x = R.fill_random_(gpu.ROCArray(np.float32, n), R.UNIFORM11, seed=4, stream_id=0)
+    r = gpu.ROCArray(np.float32, n)
+    bc = gpu.broadcast
+    gpu.materialize_(r, x.dot * x.dot + bc.exp(-bc.abs_(x)))
+    for s, e in ((0, 4096), ((1 << 31) - 2048, (1 << 31) + 2048), ((1 << 32) - 4096, n)):
+        xs = R.host_uniform11(4, 0, s, e - s)
+        assert np.array_equal(x.view(s, e).to_host(), xs)
+        want = orc.broadcast(("add", ("mul", xs, xs), ("exp", ("neg", ("abs", xs)))))
+        assert np.allclose(r.view(s, e).to_host(), want, rtol=1e-6, atol=3e-7), (s, e)
+    total = float(gpu.sum(r, f="abs2"))
+    cut = (1 << 31) + 12
+    parts = float(gpu.sum(r.view(0, cut), f="abs2")) + float(gpu.sum(r.view(cut, n), f="abs2"))
+    assert abs(total - parts) <= 1e-5 * parts
+    # U[-1,1): E[(x^2 + exp(-|x|))^2] = 1/5 + 2(2 - 5/e) + (1 - e^-2)/2 = 0.95344...
+    assert abs(total / n - (0.2 + 2 * (2 - 5 / np.e) + (1 - np.exp(-2.0)) / 2)) < 1e-3

@@ -37,3 +37,30 @@ def test_reverse(gpu):
     assert np.array_equal(gpu.reverse_(ad, dims=3).to_host(), a[:, :, ::-1])
     with pytest.raises(ValueError):
         gpu.reverse(ad, dims=4)
+
+
+def test_compaction_checks_its_positions(gpu):
+    """Through the C ABI with a destination one element too short and with positions that do not
+    belong to the mask: the kernel skips the stores it may not make and the next synchronisation
+    reports B200_INVALID_ARG; nothing is written out of bounds, the context stays usable."""
+    import ctypes as C
+    L = gpu._lib
+    mask = np.array([1, 0, 1, 1, 0, 1], dtype=bool)
+    pos = np.cumsum(mask).astype(np.int64)
+    md, pd_ = gpu.ROCArray.from_host(mask), gpu.ROCArray.from_host(pos)
+    guard = gpu.ROCArray(np.int64, 8).fill_(-7)
+    short = guard.view(0, 3)                       # 4 true entries, room for 3
+    ty, tb, ti = short.tensor(), md.tensor(), pd_.tensor()
+    assert L.lib.b200_compact(gpu.current_stream().handle, C.byref(ty), C.byref(tb), C.byref(ti), None) == L.OK
+    with pytest.raises(gpu.B200Error) as ei:
+        gpu.synchronize()
+    assert ei.value.code == L.INVALID_ARG
+    assert np.array_equal(guard.to_host(), [1, 3, 4, -7, -7, -7, -7, -7])
+    bad = gpu.ROCArray.from_host(np.array([0, 0, -3, 99, 0, 2], dtype=np.int64))
+    full = gpu.ROCArray(np.int64, 4).fill_(-7)
+    ty, ti = full.tensor(), bad.tensor()
+    assert L.lib.b200_compact(gpu.current_stream().handle, C.byref(ty), C.byref(tb), C.byref(ti), None) == L.OK
+    with pytest.raises(gpu.B200Error):
+        gpu.synchronize()
+    assert np.array_equal(full.to_host(), [-7, 6, -7, -7])
+    assert np.array_equal(gpu.findall(md).to_host(), [1, 3, 4, 6])

@@ -103,12 +103,29 @@ def test_dims_reductions(gpu, orc, dt):
                 assert_close(got, ref, tol, (dt, shape, dims, f, op), atol=1e-7 if dt.itemsize == 2 and f == "abs2" else 1e-30)
 
 
-def test_nan_and_signed_zero(gpu):
+def test_nan_and_signed_zero(gpu, orc):
     x = np.array([1.0, -3.0, np.nan, 2.0] * 1000, dtype=np.float32)
     xd = gpu.ROCArray.from_host(x)
     assert np.isnan(gpu.maximum(xd)) and np.isnan(gpu.minimum(xd)) and np.isnan(gpu.sum(xd))
     z = gpu.ROCArray.from_host(np.array([-0.0, 0.0, -0.0], dtype=np.float32))
     assert not np.signbit(gpu.maximum(z)) and np.signbit(gpu.minimum(z))
+    # against the oracle, bit for bit: zeros of both signs in long vectors and along both dimensions
+    rng = np.random.default_rng(12)
+    for dt in (np.float32, np.float64, np.float16):
+        zeros = np.where(rng.random(70_001) < 0.5, 0.0, -0.0).astype(dt)
+        for v in (zeros, np.full(70_001, -0.0, dtype=dt), np.full(33, 0.0, dtype=dt)):
+            vd = gpu.ROCArray.from_host(v)
+            for op, fn in (("max", gpu.maximum), ("min", gpu.minimum)):
+                want = np.asarray(orc.mapreduce("identity", op, v)).astype(dt).reshape(-1)[0]
+                got = dt(fn(vd))
+                assert got == 0 and np.signbit(got) == np.signbit(want), (dt, op)
+        m = np.where(rng.random((300, 70)) < 0.3, 0.0, -0.0).astype(dt)
+        md = gpu.ROCArray.from_host(m)
+        for dims, rshape in ((1, (1, 70)), (2, (300, 1))):
+            for op, fn in (("max", gpu.maximum), ("min", gpu.minimum)):
+                want = np.asarray(orc.mapreducedim("identity", op, rshape, m)).astype(dt)
+                got = fn(md, dims=dims).to_host()
+                assert np.array_equal(np.signbit(got), np.signbit(want)) and not got.any(), (dt, dims, op)
     with pytest.raises(ValueError):
         gpu.maximum(gpu.ROCArray(np.float32, 0))
     assert gpu.sum(gpu.ROCArray(np.float32, 0)) == 0 and gpu.prod(gpu.ROCArray(np.int32, 0)) == 1

@@ -115,3 +115,51 @@ def test_bounded_wait_reports_timeout_and_context_survives(gpu):
     x = gpu.ROCArray.from_host(np.arange(100_000, dtype=np.int32))
     assert np.array_equal(gpu.cumsum(x).to_host(), np.cumsum(np.arange(100_000, dtype=np.int32), dtype=np.int32))
     assert gpu.sum(x) == 100_000 * 99_999 // 2
+
+
+def test_buffer_moves_between_streams_in_order(gpu, orc):
+    """An array written on one stream and read on another needs no explicit synchronisation: the
+    operator hands the buffer over (event on the old stream, wait on the new one), which is what
+    take_ownership! does in the reference (src/memory.jl:431-446) with a host-side sync."""
+    a, b = gpu.Stream(0), gpu.Stream(0)
+    n = 1 << 24
+    ref = None
+    for it in range(100):
+        x = gpu.ROCArray(np.float32, n, stream=a)
+        x.fill_(np.float32(1.0 + it), a)                         # long fill on stream a
+        gpu.materialize_(x, x.dot * np.float32(0.5), a)          # and a dependent kernel behind it
+        r = gpu.ROCArray(np.float32, 1, stream=b)
+        gpu.mapreducedim_("identity", "+", r, x, init=np.float32(0), stream=b)     # read on stream b, no sync
+        assert x.buf.stream is b
+        got = float(r.to_host(b)[0])
+        ref = n * (1.0 + it) * 0.5
+        assert got == ref, (it, got, ref)
+    # free follows the last user: drop on b while b still reads, reallocate on a, contents intact
+    y = gpu.ROCArray(np.float32, n, stream=a).fill_(np.float32(3), a)
+    total = gpu.ROCArray(np.float32, 1, stream=b)
+    gpu.mapreducedim_("identity", "+", total, y, init=np.float32(0), stream=b)
+    del y                                                        # stream-ordered free on b, behind the reduction
+    z = gpu.ROCArray(np.float32, n, stream=a).fill_(np.float32(-1), a)
+    assert float(total.to_host(b)[0]) == 3.0 * n
+    assert float(gpu.sum(z)) == -1.0 * n
+    a.synchronize(); b.synchronize()
+
+
+def test_reclaim_returns_operator_scratch(gpu):
+    """Operator scratch (radix double buffers, scan descriptors) belongs to the stream; reclaim
+    hands it back, and live bytes return to what the arrays themselves hold."""
+    gpu.synchronize()
+    gpu.reclaim()
+    base = gpu.pool_stats()["live_bytes"]
+    n = 1 << 26
+    keys = gpu.random.fill_random_(gpu.ROCArray(np.uint32, n), gpu.random.RAWBITS, seed=3)
+    gpu.sort_(keys)
+    gpu.cumsum(gpu.ROCArray(np.int32, 1 << 22).fill_(1)).unsafe_free_()
+    gpu.synchronize()
+    assert gpu.pool_stats()["live_bytes"] >= base + 4 * n + 4 * n      # the keys and the sort's second buffer
+    keys.unsafe_free_()
+    gpu.reclaim()
+    assert gpu.pool_stats()["live_bytes"] == base
+    # scratch comes back on demand
+    x = gpu.ROCArray.from_host(np.arange(1 << 21, dtype=np.int32))
+    assert int(gpu.cumsum(x).to_host()[-1]) == (1 << 21) * ((1 << 21) - 1) // 2

@@ -100,3 +100,39 @@ def test_generator_pin(pkg):
     assert np.array_equal(a[40:50], b) and a.min() >= 0 and a.max() < 1
     i = pkg.random.host_integers(2, 0, 0, 10_000, -100, 100)
     assert i.min() >= -100 and i.max() <= 100 and i.dtype == np.int32
+
+
+def test_signed_zero_in_max_min_reductions(orc):
+    """Base.max/min order -0.0 below +0.0; the oracle's reductions must say which zero comes out."""
+    pz, nz = np.float32(0.0), np.float32(-0.0)
+    sign = lambda v: bool(np.signbit(np.asarray(v).reshape(-1)[0]))
+    assert not sign(orc.mapreduce("identity", "max", np.array([nz, pz, nz], np.float32)))
+    assert sign(orc.mapreduce("identity", "max", np.array([nz, nz], np.float32)))
+    assert sign(orc.mapreduce("identity", "min", np.array([pz, nz, pz], np.float32)))
+    assert not sign(orc.mapreduce("identity", "min", np.array([pz, pz], np.float32)))
+    m = np.array([[nz, pz], [nz, nz]], np.float32)
+    assert [bool(s) for s in np.signbit(orc.mapreducedim("identity", "max", (2, 1), m)).reshape(-1)] == [False, True]
+    assert np.isnan(orc.mapreduce("identity", "max", np.array([1.0, np.nan, 0.0], np.float32)))
+
+
+def test_torch_cpu_is_a_third_opinion(orc):
+    """torch's CPU kernels (Float64 sum and cumsum, stable sort) as an implementation that shares no
+    code with the oracle or with NumPy's reductions."""
+    import torch
+    rng = np.random.default_rng(3)
+    x = (rng.random(300_007) * 2 - 1).astype(np.float32)
+    tx = torch.from_numpy(x).double()
+    assert abs(orc.mapreduce("identity", "+", x) - float(tx.sum())) <= 1e-9 * float(tx.abs().sum())
+    assert abs(orc.mapreduce("abs2", "+", x) - float((tx * tx).sum())) <= 1e-9 * float((tx * tx).sum())
+    assert np.allclose(orc.accumulate("+", x), torch.cumsum(tx, 0).numpy(), rtol=1e-12, atol=1e-9)
+    iv = rng.integers(-100, 101, 100_003).astype(np.int32)
+    assert np.array_equal(orc.accumulate("+", iv), torch.cumsum(torch.from_numpy(iv), 0, dtype=torch.int32).numpy())
+    k = rng.integers(0, 1000, 50_001).astype(np.int64)             # many ties: stability matters
+    vals, idx = torch.sort(torch.from_numpy(k), stable=True)
+    assert np.array_equal(orc.sort(k), vals.numpy()) and np.array_equal(orc.sortperm(k), idx.numpy() + 1)
+    f = rng.standard_normal(20_001).astype(np.float32)
+    f[::40] = f[3]
+    vals, idx = torch.sort(torch.from_numpy(f), stable=True)
+    assert np.array_equal(orc.sort(f), vals.numpy()) and np.array_equal(orc.sortperm(f), idx.numpy() + 1)
+    vals, idx = torch.sort(torch.from_numpy(f), stable=True, descending=True)
+    assert np.array_equal(orc.sort(f, rev=True), vals.numpy()) and np.array_equal(orc.sortperm(f, rev=True), idx.numpy() + 1)

@@ -15,11 +15,11 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _scan(gpu, fn, out, src, op, init, dim=0):
+def _scan(gpu, fn, out, src, op, init, dim=0, inclusive=1):
     L = gpu._lib
     tb, ta = out.tensor(), src.tensor()
     ib = None if init is None else np.asarray(init, dtype=src.dtype).tobytes()
-    return fn(gpu.current_stream().handle, C.byref(tb), C.byref(ta), op, ib, dim, 1)
+    return fn(gpu.current_stream().handle, C.byref(tb), C.byref(ta), op, ib, dim, inclusive)
 
 
 def test_noalloc_scan_matches_regular_entry_point(gpu):
@@ -56,6 +56,29 @@ def test_noalloc_scan_matches_regular_entry_point(gpu):
         assert _scan(gpu, regular, a, src, L.RED_ADD, None, dim) == L.OK
         assert _scan(gpu, noalloc, b, src, L.RED_ADD, None, dim) == L.OK
         assert np.array_equal(a.to_host(), b.to_host()) and np.array_equal(b.to_host(), np.cumsum(m, axis=dim))
+
+
+def test_noalloc_scan_other_forms(gpu):
+    """Exclusive scans, a max-scan, Float16 elements (tiles of 8192) and the shape that needs no
+    bookkeeping at all (columns of at most 32 elements, one thread per column)."""
+    L = gpu._lib
+    regular, noalloc = L.lib.b200_accumulate, L.lib.b200_accumulate_noalloc
+    rng = np.random.default_rng(1)
+    cases = (
+        (rng.integers(-100, 101, 200_003).astype(np.int32), L.RED_ADD, np.int32(5), 0, 0),      # exclusive
+        (rng.standard_normal(100_001).astype(np.float32), L.RED_MAX, None, 0, 1),                # max-scan
+        (np.where(np.arange(70_000) % 2 == 0, 1, -1).astype(np.float16), L.RED_ADD, None, 0, 1),  # 16-bit tiles
+        (rng.integers(-9, 10, (20, 2048)).astype(np.int64), L.RED_ADD, None, 0, 1),              # short columns
+        (rng.integers(-9, 10, (20, 2048)).astype(np.int64), L.RED_ADD, np.int64(3), 0, 0),
+    )
+    for x, op, init, dim, inclusive in cases:
+        src = gpu.ROCArray.from_host(x)
+        a, b = gpu.ROCArray(x.dtype, x.shape), gpu.ROCArray(x.dtype, x.shape)
+        assert _scan(gpu, regular, a, src, op, init, dim, inclusive) == L.OK, L.last_error()
+        allocs = gpu.pool_stats()["alloc_count"]
+        assert _scan(gpu, noalloc, b, src, op, init, dim, inclusive) == L.OK, L.last_error()
+        assert gpu.pool_stats()["alloc_count"] == allocs
+        assert np.array_equal(a.to_host(), b.to_host()), (x.dtype, x.shape, op, inclusive)
 
 
 def test_noalloc_scan_refuses_oversized_input(gpu):
