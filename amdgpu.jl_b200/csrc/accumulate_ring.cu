@@ -4,21 +4,21 @@
 // for the long 1-D case.  One block per SM, specialised warps around a ring of shared-memory
 // stages:
 //   * the producer (one thread) takes tile numbers from an atomic ticket and fills free stages
-//     with bulk asynchronous copies (cp.async.bulk + mbarrier transaction counts), never more than
-//     a bounded number of tiles in flight - the copies of an SM share its path to L2 with the
-//     descriptor reads below, and a deep queue of copies makes those reads slow;
+//     with bulk asynchronous copies (cp.async.bulk + mbarrier transaction counts), a bounded
+//     number of tiles in flight;
 //   * 16 consumer warps run two phases per tile, `lead` tiles apart: phase A reduces a tile that
-//     has just landed (per-warp totals stay in shared memory) and publishes its aggregate; phase C,
-//     `lead` tiles later, scans the tile out of shared memory with the resolved prefix and streams
-//     the result to HBM;
-//   * the look-back warp resolves prefixes in the gap: it reads up to 512 predecessor descriptors
-//     per round trip (all ranks of a round publish at about the same time, so the nearest full
-//     prefix is one to three rounds of blocks back), publishes the tile's inclusive prefix and
-//     hands the exclusive one to the consumers through shared memory.
-// Descriptors are 64-bit words {tag:32 | value:32}; the tag carries the launch number, so words
-// of earlier launches read as empty and nothing is cleared between launches.  Every wait (mbarrier
-// or descriptor) is bounded; a wait that runs out latches B200_LOOKBACK_TIMEOUT, all roles leave,
-// and the block drains its copies before it returns.
+//     has just landed (per-warp totals stay in shared memory) and publishes the tile's aggregate;
+//     phase C scans the tile out of shared memory with its prefix and streams the result to HBM;
+//   * four prefix warps, one tile each in rotation, compute the prefixes.  A block knows the
+//     inclusive prefix of its own previous tile, so the prefix of its next tile only needs the
+//     AGGREGATES of the tiles in between (about one per other block), never another block's
+//     resolved prefix: there is no chain of dependent waits across blocks.  A prefix warp starts
+//     reading those aggregates as soon as the producer holds the ticket, while the tile's own
+//     data is still on its way.
+// Descriptors are 64-bit words {launch number:32 | aggregate:32}; words of earlier launches read
+// as empty, nothing is cleared between launches.  Every wait (mbarrier or descriptor) is bounded;
+// a wait that runs out latches B200_LOOKBACK_TIMEOUT, all roles leave, and the block drains its
+// copies before it returns.
 #include "scan_common.cuh"
 
 #include <cstdlib>
@@ -27,9 +27,10 @@ namespace b200 {
 
 constexpr int kRingConsumerWarps = 16;
 constexpr int kRingConsumers = kRingConsumerWarps * 32;
-constexpr int kRingThreads = kRingConsumers + 64;        // + producer warp + look-back warp
+constexpr int kRingPrefixWarps = 4;
+constexpr int kRingThreads = kRingConsumers + 32 + 32 * kRingPrefixWarps;   // + producer warp + prefix warps
 constexpr int kRingBytes = 192 * 1024;                   // shared memory given to the stages
-constexpr int kRingWindows = 16;                         // look-back: 16 x 32 descriptors per round trip
+constexpr int kRingWindows = 8;                          // aggregates are gathered 8 x 32 at a time
 
 struct RingPlan {
     int64_t  nvec;            // 16-byte vectors in the array
@@ -103,62 +104,55 @@ struct RingShared {
     static constexpr int kStages = kRingBytes / kTileBytes;
     static constexpr int kTotals = NV * kRingConsumerWarps;
     alignas(128) unsigned char stage[kStages][kTileBytes];
-    uint64_t  full[kStages], empty[kStages], aggready[kStages], resolved[kStages];
+    uint64_t  full[kStages], empty[kStages], aggready[kStages], resolved[kStages], ticketed[kStages];
     long long tile_of[kStages];
+    long long tiles[2 * kStages];          // tile numbers of the last 2 x stages local tiles (prefix warps)
+    long long last_local;                  // local index at which the producer ran out of tiles (-1: not yet)
     Acc       agg[kStages], prefix[kStages];
     Acc       wtot[kStages][kTotals];      // inclusive totals of (vector row j, warp w), phase A
     Acc       wex[kStages][kTotals];       // their exclusive scan in element order
     int       abort;
 };
 
-// Exclusive prefix of tile t > 0: fold of the aggregates of tiles t-1, t-2, ... down to the nearest
-// tile that has published its inclusive prefix.  Whole warp; the result is valid in every lane.
+// Fold of the aggregates of tiles lo .. hi-1 in tile order (identity for an empty range).  Whole
+// warp; the result is valid in every lane.  Waits (bounded) for aggregates that are not out yet.
 template <typename Acc, int OP>
-__device__ __forceinline__ bool ring_lookback(const unsigned long long* desc, int64_t t, uint32_t epoch, uint32_t max_polls,
-                                              const int32_t* err_word, const volatile int* abort_flag, int lane, Acc* out) {
-    const uint32_t tag_a = (epoch << 2) | FLAG_AGGREGATE, tag_p = (epoch << 2) | FLAG_PREFIX;
-    const unsigned long long none = ((unsigned long long)tag_p << 32) | acc_bits(scan_identity<Acc, OP>());
+__device__ __forceinline__ bool ring_gather(const unsigned long long* desc, int64_t lo, int64_t hi, uint32_t epoch,
+                                            uint32_t max_polls, const int32_t* err_word, const volatile int* abort_flag,
+                                            int lane, Acc* out) {
     Acc running = scan_identity<Acc, OP>();
-    bool have = false;
     uint32_t polls = 0;
-    for (int64_t base = t - 1;; base -= 32 * kRingWindows) {
+    for (int64_t base = hi - 1; base >= lo; base -= 32 * kRingWindows) {
         unsigned long long w[kRingWindows];
 #pragma unroll
         for (int k = 0; k < kRingWindows; ++k) {
             const int64_t idx = base - 32 * k - lane;
-            w[k] = idx >= 0 ? desc_load(desc + idx) : none;      // before the array: an empty prefix ends the walk
+            w[k] = idx >= lo ? desc_load(desc + idx) : 0ull;
         }
 #pragma unroll
         for (int k = 0; k < kRingWindows; ++k) {
+            if (base - 32 * k < lo) break;               // uniform: this window lies before the range
             const int64_t idx = base - 32 * k - lane;
             unsigned long long cur = w[k];
-            int stop;
             while (true) {
-                const uint32_t tag = (uint32_t)(cur >> 32);
-                const int state = tag == tag_p ? 2 : (tag == tag_a ? 1 : 0);
-                const uint32_t pmask = __ballot_sync(0xffffffffu, state == 2);
-                const uint32_t emask = __ballot_sync(0xffffffffu, state == 0);
-                stop = pmask ? (__ffs(pmask) - 1) : 32;
-                const uint32_t need = stop >= 31 ? 0xffffffffu : ((2u << stop) - 1u);
-                if ((emask & need) == 0) break;
-                // a predecessor that is needed has not published yet
+                const bool missing = idx >= lo && (uint32_t)(cur >> 32) != epoch;
+                if (!__any_sync(0xffffffffu, missing)) break;
                 if (++polls > max_polls) return false;
                 if ((polls & 255u) == 0 && (error_latched(err_word) || *abort_flag)) return false;
                 __nanosleep(40);
-                if (state == 0) cur = desc_load(desc + idx);
+                if (missing) cur = desc_load(desc + idx);
             }
-            Acc contrib = lane <= stop ? acc_from<Acc>((uint32_t)cur) : scan_identity<Acc, OP>();
+            Acc contrib = idx >= lo ? acc_from<Acc>((uint32_t)cur) : scan_identity<Acc, OP>();
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {             // lane 0 ends with farthest (+) ... (+) nearest
                 const Acc far = __shfl_down_sync(0xffffffffu, contrib, o);
                 if (lane + o < 32) contrib = scan_apply<Acc, OP>(far, contrib);
             }
-            const Acc window = __shfl_sync(0xffffffffu, contrib, 0);
-            running = have ? scan_apply<Acc, OP>(window, running) : window;
-            have = true;
-            if (stop < 32) { *out = running; return true; }
+            running = scan_apply<Acc, OP>(__shfl_sync(0xffffffffu, contrib, 0), running);
         }
     }
+    *out = running;
+    return true;
 }
 
 template <typename T, int OP, int NV>
@@ -185,8 +179,10 @@ scan_ring_kernel(const T* A, T* B, RingPlan pl, unsigned long long* desc, unsign
             mbar_init(&sm.empty[s], kRingConsumerWarps);
             mbar_init(&sm.aggready[s], 1);
             mbar_init(&sm.resolved[s], 1);
+            mbar_init(&sm.ticketed[s], 1);
         }
         sm.abort = 0;
+        sm.last_local = -1;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (blockIdx.x == 0) tickets[(pl.epoch + 1u) & 1u] = 0;
@@ -219,10 +215,15 @@ scan_ring_kernel(const T* A, T* B, RingPlan pl, unsigned long long* desc, unsign
                 }
                 if ((int64_t)t >= pl.ntiles) {   // no tile left: tell the other roles
                     sm.tile_of[s] = -1;
+                    sm.tiles[i % (2 * S)] = -1;
+                    *(volatile long long*)&sm.last_local = i;
+                    mbar_arrive(&sm.ticketed[s]);
                     mbar_arrive(&sm.full[s]);
                     break;
                 }
                 sm.tile_of[s] = (long long)t;
+                sm.tiles[i % (2 * S)] = (long long)t;
+                mbar_arrive(&sm.ticketed[s]);    // the prefix warp of this tile may start gathering
                 const uint32_t bytes = (uint32_t)tile_vecs(t) * 16u;
                 mbar_arrive_expect_tx(&sm.full[s], bytes);
                 bulk_load(sm.stage[s], reinterpret_cast<const unsigned char*>(A) + (int64_t)t * TILE_VECS * 16, bytes, &sm.full[s], stream);
@@ -230,30 +231,44 @@ scan_ring_kernel(const T* A, T* B, RingPlan pl, unsigned long long* desc, unsign
                 t = atomicAdd(ticket, 1u);       // the next ticket travels while this thread waits for a stage
             }
         }
-    } else if (warp == kRingConsumerWarps + 1) {
-        // ---------------------------------------------------------------- look-back warp
-        for (int64_t i = 0;; ++i) {
+    } else if (warp > kRingConsumerWarps) {
+        // ---------------------------------------------------------------- prefix warps
+        // local tile i belongs to prefix warp i mod 4; its exclusive prefix is
+        //   (inclusive prefix of local tile i-1)  (+)  aggregates of the tiles between the two
+        for (int64_t i = warp - kRingConsumerWarps - 1;; i += kRingPrefixWarps) {
             const int s = (int)(i % S);
             const uint32_t par = (uint32_t)(i / S) & 1u;
-            if (!mbar_wait(&sm.full[s], par, abort_flag, budget)) { if (lane == 0) give_up(); break; }
-            const int64_t t = sm.tile_of[s];
+            // the producer stops at some local index; prefix warps whose next tile lies beyond it leave
+            bool ticket = false, over = false;
+            for (uint32_t tries = 0; !(ticket = mbar_try_wait(&sm.ticketed[s], par)); ++tries) {
+                const long long last = *(volatile long long*)&sm.last_local;
+                if (last >= 0 && i > last) { over = true; break; }
+                if (tries > budget || *abort_flag) break;
+            }
+            if (over) break;
+            if (!ticket) { if (lane == 0) give_up(); break; }
+            const int64_t t = sm.tiles[i % (2 * S)];
             if (t < 0) break;
-            if (!mbar_wait(&sm.aggready[s], par, abort_flag, budget)) { if (lane == 0) give_up(); break; }
-            Acc prefix = scan_identity<Acc, OP>();
-            if (t == 0) {
-                if (pl.has_init) prefix = (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
+            const int64_t t_prev = i > 0 ? sm.tiles[(i - 1) % (2 * S)] : -1;
+            Acc between;
+            if (!ring_gather<Acc, OP>(desc, t_prev + 1, t, pl.epoch, pl.max_polls, err_word, abort_flag, lane, &between)) {
+                if (lane == 0) give_up();
+                break;
+            }
+            Acc base = scan_identity<Acc, OP>();
+            if (i == 0) {
+                if (pl.has_init) base = (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
             } else {
-                if (!ring_lookback<Acc, OP>(desc, t, pl.epoch, pl.max_polls, err_word, abort_flag, lane, &prefix)) {
+                const int sp = (int)((i - 1) % S);
+                const uint32_t pp = (uint32_t)((i - 1) / S) & 1u;
+                if (!mbar_wait(&sm.resolved[sp], pp, abort_flag, budget) || !mbar_wait(&sm.aggready[sp], pp, abort_flag, budget)) {
                     if (lane == 0) give_up();
                     break;
                 }
-                if (lane == 0) {
-                    const Acc inclusive = scan_apply<Acc, OP>(prefix, sm.agg[s]);
-                    desc_store(desc + t, ((unsigned long long)((pl.epoch << 2) | FLAG_PREFIX) << 32) | acc_bits(inclusive));
-                }
+                base = scan_apply<Acc, OP>(sm.prefix[sp], sm.agg[sp]);
             }
             if (lane == 0) {
-                sm.prefix[s] = prefix;
+                sm.prefix[s] = scan_apply<Acc, OP>(base, between);
                 mbar_arrive(&sm.resolved[s]);
             }
             __syncwarp();
@@ -310,17 +325,7 @@ scan_ring_kernel(const T* A, T* B, RingPlan pl, unsigned long long* desc, unsign
                 }
                 if (lane == 31) {
                     sm.agg[s] = inc;
-                    // publish at once: successors need the aggregate, not this tile's own prefix
-                    if (t == 0) {
-                        Acc first = inc;
-                        if (pl.has_init) {
-                            const Acc seed = (pl.has_init == 2) ? scan_up<T>(*reinterpret_cast<const T*>(pl.init_dev)) : as_c<Acc, uint64_t>(pl.init);
-                            first = scan_apply<Acc, OP>(seed, inc);
-                        }
-                        desc_store(desc, ((unsigned long long)((pl.epoch << 2) | FLAG_PREFIX) << 32) | acc_bits(first));
-                    } else {
-                        desc_store(desc + t, ((unsigned long long)((pl.epoch << 2) | FLAG_AGGREGATE) << 32) | acc_bits(inc));
-                    }
+                    desc_store(desc + t, ((unsigned long long)pl.epoch << 32) | acc_bits(inc));   // at once: other blocks wait for it
                 }
                 __syncwarp();
                 if (lane == 31) mbar_arrive(&sm.aggready[s]);
@@ -431,7 +436,7 @@ static int32_t launch_ring(b200_stream_t st, const void* A, void* B, const ScanP
     rp.max_polls = pl.max_polls;
     rp.init = pl.init;
     rp.init_dev = pl.init_dev;
-    static const int lead = env_int("B200_SCAN_RING_LEAD", 3);
+    static const int lead = env_int("B200_SCAN_RING_LEAD", 4);
     static const int inflight = env_int("B200_SCAN_RING_INFLIGHT", 2);
     rp.lead = lead;
     rp.inflight = inflight;
@@ -467,7 +472,7 @@ static int32_t launch_ring_op(b200_stream_t st, int op, const void* A, void* B, 
 }
 
 int32_t launch_scan_ring(b200_stream_t st, int32_t dtype, int32_t op, const void* A, void* B, const ScanPlan& pl) {
-    static const int enabled = env_int("B200_SCAN_RING", 1);
+    static const int enabled = env_int("B200_SCAN_RING", 0);
     static const int nv = env_int("B200_SCAN_RING_VECS", 4);
     if (!enabled) return B200_UNSUPPORTED;
     if (pl.K != 1 || pl.M != 1) return B200_UNSUPPORTED;
