@@ -22,7 +22,7 @@ from .mapreduce import prepared as mapreduce_prepared
 from .accumulate import accumulate_, accumulate, cumsum, cumprod
 from .accumulate import prepared as accumulate_prepared
 from .sorting import sort_, sort, sortperm_, sortperm
-from .indexing import findall, getindex, getindex_mask, reverse, reverse_
+from .indexing import findall, getindex, getindex_mask, getindex_mask_dim, reverse, reverse_
 from . import random
 from . import graph
 from .graph import Graph, GraphExec, capture, instantiate, launch, update, is_capturing, captured

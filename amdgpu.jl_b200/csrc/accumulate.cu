@@ -34,54 +34,89 @@ constexpr int kScanWarps = kScanThreads / 32;
 static_assert(kScanVecs * kScanWarps == 32, "warp totals must fill exactly one warp");
 
 // ---- tile descriptors ---------------------------------------------------------------------------------
-// 4-byte accumulators: one 64-bit word {flag:32 | value:32}, written and read with single accesses.
-// 8-byte accumulators: flag word plus two value slots, ordered by fences.
+// Every descriptor is a 64-bit word whose upper half is a tag, (launch number << 2) | state, so
+// that words written by earlier launches read as EMPTY and the words never have to be cleared
+// between launches (launch number 0: the caller cleared them).  The words of a stream live in a
+// buffer that holds nothing but such words (b200::scan_state), whatever kernel wrote them.
+// 4-byte accumulators: the lower half of the word is the value, one access publishes both.
+// 8-byte accumulators: the values sit in two arrays beside the words, ordered by fences.
+__device__ __forceinline__ uint32_t tag_state(unsigned long long w, uint32_t epoch) {
+    const uint32_t tag = (uint32_t)(w >> 32);
+    return (tag >> 2) == epoch ? (tag & 3u) : FLAG_EMPTY;
+}
+__device__ __forceinline__ unsigned long long tag_word(uint32_t epoch, uint32_t state, uint32_t low = 0) {
+    return ((unsigned long long)((epoch << 2) | state) << 32) | low;
+}
+
 template <typename Acc, bool SMALL = (sizeof(Acc) == 4)>
 struct TileState;
 
 template <typename Acc>
 struct TileState<Acc, true> {
     unsigned long long* words;
-    static size_t bytes(int64_t ntiles) { return (size_t)ntiles * 8; }
-    __host__ __device__ void bind(void* p, int64_t) { words = reinterpret_cast<unsigned long long*>(p); }
+    uint32_t epoch;
+    static size_t flag_bytes(int64_t ntiles) { return (size_t)ntiles * 8; }
+    static size_t value_bytes(int64_t) { return 0; }
+    __host__ __device__ void bind(void* flag_mem, void*, int64_t, uint32_t e) {
+        words = reinterpret_cast<unsigned long long*>(flag_mem);
+        epoch = e;
+    }
     __device__ __forceinline__ void publish(int64_t t, uint32_t flag, Acc v) {
         uint32_t bits;
         memcpy(&bits, &v, 4);
-        *reinterpret_cast<volatile unsigned long long*>(words + t) = ((unsigned long long)flag << 32) | bits;
+        *reinterpret_cast<volatile unsigned long long*>(words + t) = tag_word(epoch, flag, bits);
     }
     __device__ __forceinline__ uint32_t peek(int64_t t, Acc& v) {
         const unsigned long long w = *reinterpret_cast<volatile unsigned long long*>(words + t);
         const uint32_t bits = (uint32_t)w;
         memcpy(&v, &bits, 4);
-        return (uint32_t)(w >> 32);
+        return tag_state(w, epoch);
     }
 };
 
 template <typename Acc>
 struct TileState<Acc, false> {
-    uint32_t* flags;
+    unsigned long long* flags;
     Acc* agg;
     Acc* pre;
-    static size_t bytes(int64_t ntiles) { return (size_t)ntiles * (8 + 8 + 8); }
-    __host__ __device__ void bind(void* p, int64_t ntiles) {
-        agg = reinterpret_cast<Acc*>(p);
+    uint32_t epoch;
+    static size_t flag_bytes(int64_t ntiles) { return (size_t)ntiles * 8; }
+    static size_t value_bytes(int64_t ntiles) { return (size_t)ntiles * 16; }
+    __host__ __device__ void bind(void* flag_mem, void* value_mem, int64_t ntiles, uint32_t e) {
+        flags = reinterpret_cast<unsigned long long*>(flag_mem);
+        agg = reinterpret_cast<Acc*>(value_mem);
         pre = agg + ntiles;
-        flags = reinterpret_cast<uint32_t*>(pre + ntiles);
+        epoch = e;
     }
     __device__ __forceinline__ void publish(int64_t t, uint32_t flag, Acc v) {
         if (flag == FLAG_AGGREGATE) *reinterpret_cast<volatile Acc*>(agg + t) = v;
         else *reinterpret_cast<volatile Acc*>(pre + t) = v;
         __threadfence();
-        *reinterpret_cast<volatile uint32_t*>(flags + t) = flag;
+        *reinterpret_cast<volatile unsigned long long*>(flags + t) = tag_word(epoch, flag);
     }
     __device__ __forceinline__ uint32_t peek(int64_t t, Acc& v) {
-        const uint32_t f = *reinterpret_cast<volatile uint32_t*>(flags + t);
+        const uint32_t f = tag_state(*reinterpret_cast<volatile unsigned long long*>(flags + t), epoch);
         if (f == FLAG_EMPTY) return f;
         __threadfence();
         v = (f == FLAG_AGGREGATE) ? *reinterpret_cast<volatile Acc*>(agg + t) : *reinterpret_cast<volatile Acc*>(pre + t);
         return f;
     }
 };
+
+// Descriptor words (in the stream's tagged buffer) and value storage (stream scratch) of one launch.
+template <typename Acc>
+static int32_t descriptor_storage(b200_stream_t st, int64_t ntiles, void** flag_mem, void** value_mem, uint32_t* epoch) {
+    void* state = nullptr;
+    bool must_clear = false;
+    const size_t fbytes = TileState<Acc>::flag_bytes(ntiles);
+    B200_TRY(scan_state(st, fbytes, &state, epoch, &must_clear));
+    *flag_mem = reinterpret_cast<unsigned char*>(state) + kScanStateHeader;
+    // a replayed graph repeats its launch number: a captured launch clears its words itself
+    if (must_clear) B200_CUDA(cudaMemsetAsync(*flag_mem, 0, fbytes, st->s));
+    *value_mem = nullptr;
+    if (TileState<Acc>::value_bytes(ntiles)) B200_TRY(scratch(st, TileState<Acc>::value_bytes(ntiles), value_mem));
+    return B200_OK;
+}
 
 template <typename T, int OP>
 __global__ void __launch_bounds__(kScanThreads)
@@ -101,7 +136,7 @@ scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned in
     __shared__ int s_abort;
 
     TileState<Acc> state;
-    state.bind(state_mem, pl.ntiles);
+    state.bind(state_mem, pl.value_mem, pl.ntiles, pl.epoch);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -295,6 +330,8 @@ struct SegPlan {
     uint32_t max_polls;
     uint64_t init;
     const void* init_dev;
+    uint32_t epoch;
+    void* value_mem;
 };
 
 template <typename T, int OP>
@@ -313,7 +350,7 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
     __shared__ int s_verdict, s_abort;
 
     TileState<Acc> state;
-    state.bind(state_mem, pl.nsegs);
+    state.bind(state_mem, pl.value_mem, pl.nsegs, pl.epoch);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint4* src = reinterpret_cast<const uint4*>(A);
     uint4* dst = reinterpret_cast<uint4*>(B);
@@ -581,13 +618,14 @@ struct StridedScanPlan {
     int64_t ntiles;           // M * S * NT
     int32_t inclusive, has_init;
     uint32_t max_polls;
+    uint32_t epoch;
     uint64_t init;
     const void* init_dev;
 };
 
 template <typename T, int OP, int VEC>
 __global__ void __launch_bounds__(256)
-scan_strided_kernel(const T* A, T* B, StridedScanPlan pl, uint32_t* flags, typename ScanAcc<T>::type* agg,
+scan_strided_kernel(const T* A, T* B, StridedScanPlan pl, unsigned long long* flags, typename ScanAcc<T>::type* agg,
                     typename ScanAcc<T>::type* pre, unsigned int* ticket, int32_t* err_word) {
     using Acc = typename ScanAcc<T>::type;
     using VT = Vec<T, VEC>;
@@ -657,18 +695,18 @@ scan_strided_kernel(const T* A, T* B, StridedScanPlan pl, uint32_t* flags, typen
         __threadfence();
     }
     __syncthreads();
-    if (tid == 0) *reinterpret_cast<volatile uint32_t*>(flags + d) = (tt == 0) ? FLAG_PREFIX : FLAG_AGGREGATE;
+    if (tid == 0) *reinterpret_cast<volatile unsigned long long*>(flags + d) = tag_word(pl.epoch, (tt == 0) ? FLAG_PREFIX : FLAG_AGGREGATE);
     if (tid < KX && tt > 0) {
         Acc running = scan_identity<Acc, OP>();
         bool set = false, failed = false;
         for (int64_t p = d - 1;; --p) {                 // ends at the strip's first tile at the latest (always a full prefix)
-            uint32_t f = *reinterpret_cast<volatile uint32_t*>(flags + p);
+            uint32_t f = tag_state(*reinterpret_cast<volatile unsigned long long*>(flags + p), pl.epoch);
             uint32_t polls = 0;
             while (f == FLAG_EMPTY) {
                 ++polls;
                 if (polls > pl.max_polls || ((polls & 1023u) == 0 && error_latched(err_word))) { failed = true; break; }
                 if (polls > 32) __nanosleep(polls > 4096 ? 256 : 32);
-                f = *reinterpret_cast<volatile uint32_t*>(flags + p);
+                f = tag_state(*reinterpret_cast<volatile unsigned long long*>(flags + p), pl.epoch);
             }
             if (failed) break;
             __threadfence();
@@ -690,7 +728,7 @@ scan_strided_kernel(const T* A, T* B, StridedScanPlan pl, uint32_t* flags, typen
         if (tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
         return;
     }
-    if (tid == 0 && tt > 0) *reinterpret_cast<volatile uint32_t*>(flags + d) = FLAG_PREFIX;
+    if (tid == 0 && tt > 0) *reinterpret_cast<volatile unsigned long long*>(flags + d) = tag_word(pl.epoch, FLAG_PREFIX);
 
     // ---- offsets and stores
     const bool seeded = tt > 0 || pl.has_init;
@@ -740,17 +778,22 @@ static int32_t launch_scan_strided(b200_stream_t st, const void* A, void* B, con
     sp.max_polls = pl.max_polls;
     sp.init = pl.init;
     sp.init_dev = pl.init_dev;
-    const size_t fbytes = ((size_t)sp.ntiles * sizeof(uint32_t) + 255) / 256 * 256;
+    // flag words in the stream's tagged buffer (never cleared), the value vectors in scratch
+    const size_t fbytes = (size_t)sp.ntiles * sizeof(unsigned long long);
     const size_t vbytes = (size_t)sp.ntiles * KX * sizeof(Acc);
+    void* state = nullptr;
+    bool must_clear = false;
+    B200_TRY(scan_state(st, fbytes, &state, &sp.epoch, &must_clear));
+    unsigned long long* flags = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(state) + kScanStateHeader);
+    if (must_clear) B200_CUDA(cudaMemsetAsync(flags, 0, fbytes, st->s));
     void* scr = nullptr;
     unsigned int* counters = nullptr;
-    B200_TRY(scratch(st, fbytes + 2 * vbytes, &scr, &counters));
-    B200_CUDA(cudaMemsetAsync(scr, 0, fbytes, st->s));      // the flags; the value vectors need no clearing
+    B200_TRY(scratch(st, 2 * vbytes, &scr, &counters));
     unsigned char* base = reinterpret_cast<unsigned char*>(scr);
     unsigned int* ticket = counters + (kCounterBytes / sizeof(unsigned int) - 1);
     scan_strided_kernel<T, OP, VEC><<<(unsigned)sp.ntiles, 256, 0, st->s>>>(
-        (const T*)A, (T*)B, sp, reinterpret_cast<uint32_t*>(base), reinterpret_cast<Acc*>(base + fbytes),
-        reinterpret_cast<Acc*>(base + fbytes + vbytes), ticket, device_error_word(st->dev));
+        (const T*)A, (T*)B, sp, flags, reinterpret_cast<Acc*>(base),
+        reinterpret_cast<Acc*>(base + vbytes), ticket, device_error_word(st->dev));
     return B200_OK;
 }
 
@@ -776,16 +819,6 @@ scan_column_thread_kernel(const T* A, T* B, ScanPlan pl) {
     }
 }
 
-template <typename T> constexpr int32_t scan_dtype_code();
-template <> constexpr int32_t scan_dtype_code<float>() { return B200_F32; }
-template <> constexpr int32_t scan_dtype_code<double>() { return B200_F64; }
-template <> constexpr int32_t scan_dtype_code<int32_t>() { return B200_I32; }
-template <> constexpr int32_t scan_dtype_code<int64_t>() { return B200_I64; }
-template <> constexpr int32_t scan_dtype_code<uint32_t>() { return B200_U32; }
-template <> constexpr int32_t scan_dtype_code<uint64_t>() { return B200_U64; }
-template <> constexpr int32_t scan_dtype_code<__half>() { return B200_F16; }
-template <> constexpr int32_t scan_dtype_code<__nv_bfloat16>() { return B200_BF16; }
-
 template <typename T, int OP>
 static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl) {
     using Acc = typename ScanAcc<T>::type;
@@ -807,10 +840,6 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         return B200_OK;
     }
     if (ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {
-        // long dense vectors: the one-pass ring kernel where it applies (4-byte accumulators),
-        // else the two-pass segment kernel below
-        const int32_t ring = launch_scan_ring(st, scan_dtype_code<T>(), OP, A, B, pl);
-        if (ring != B200_UNSUPPORTED) return ring;
         SegPlan sp{};
         sp.nvec = pl.L * (int64_t)sizeof(T) / 16;
         int64_t grid = resident_blocks(scan_segment_kernel<T, OP>, kSegThreads, 0, st->dev);
@@ -829,10 +858,7 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         sp.init = pl.init;
         sp.init_dev = pl.init_dev;
         void* scr = nullptr;
-        unsigned int* counters = nullptr;
-        const size_t sbytes = TileState<Acc>::bytes(sp.nsegs);
-        B200_TRY(scratch(st, sbytes, &scr, &counters));
-        B200_CUDA(cudaMemsetAsync(scr, 0, sbytes, st->s));
+        B200_TRY(descriptor_storage<Acc>(st, sp.nsegs, &scr, &sp.value_mem, &sp.epoch));
         if (grid > sp.nsegs) grid = sp.nsegs;
         scan_segment_kernel<T, OP><<<(unsigned)grid, kSegThreads, 0, st->s>>>((const T*)A, (T*)B, sp, scr, device_error_word(st->dev));
         return B200_OK;
@@ -843,9 +869,9 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
     pl.vec_ok = (pl.K == 1 && aligned && (ncols == 1 || (pl.L * sizeof(T)) % 16 == 0)) ? 1 : 0;
     void* scr = nullptr;
     unsigned int* counters = nullptr;
-    const size_t sbytes = TileState<Acc>::bytes(pl.ntiles);
-    B200_TRY(scratch(st, sbytes, &scr, &counters));
-    B200_CUDA(cudaMemsetAsync(scr, 0, sbytes, st->s));
+    B200_TRY(descriptor_storage<Acc>(st, pl.ntiles, &scr, &pl.value_mem, &pl.epoch));
+    void* unused = nullptr;
+    B200_TRY(scratch(st, 0, &unused, &counters));
     // the last counter slot serves as the tile ticket (it returns to zero by itself)
     unsigned int* ticket = counters + (kCounterBytes / sizeof(unsigned int) - 1);
     scan_lookback_kernel<T, OP><<<(unsigned)pl.ntiles, kScanThreads, 0, st->s>>>(
@@ -911,8 +937,8 @@ static int32_t launch_scan_static(b200_stream_t st, const void* A, void* B, Scan
     }
     pl.tiles_per_col = (pl.L + TILE - 1) / TILE;
     pl.ntiles = pl.tiles_per_col * ncols;
-    const size_t state_bytes = TileState<Acc>::bytes(pl.ntiles);
-    const int64_t max_tiles = (int64_t)((kStaticScanBytes - kStaticScanHeader) / TileState<Acc>::bytes(1));
+    const size_t flag_bytes = TileState<Acc>::flag_bytes(pl.ntiles);
+    const int64_t max_tiles = (int64_t)((kStaticScanBytes - kStaticScanHeader) / (TileState<Acc>::flag_bytes(1) + TileState<Acc>::value_bytes(1)));
     if (pl.ntiles > max_tiles)
         return fail(B200_TOO_LARGE, "accumulate (no-allocation variant): %lld tiles of %d elements needed, the built-in "
                     "scratch holds %lld for this element type; use b200_accumulate for larger inputs",
@@ -921,8 +947,11 @@ static int32_t launch_scan_static(b200_stream_t st, const void* A, void* B, Scan
     B200_TRY(static_scan_scratch(st->dev, &base));
     const bool aligned = reinterpret_cast<uintptr_t>(A) % 16 == 0 && reinterpret_cast<uintptr_t>(B) % 16 == 0;
     pl.vec_ok = (pl.K == 1 && aligned && (ncols == 1 || (pl.L * sizeof(T)) % 16 == 0)) ? 1 : 0;
-    // the array keeps whatever the previous call left: ticket and descriptors must start at zero
-    B200_CUDA(cudaMemsetAsync(base, 0, kStaticScanHeader + state_bytes, st->s));
+    // the array keeps whatever the previous call left: ticket and descriptor words must start at
+    // zero (launch number 0 = "the words were cleared"); the values behind them need no clearing
+    B200_CUDA(cudaMemsetAsync(base, 0, kStaticScanHeader + flag_bytes, st->s));
+    pl.epoch = 0;
+    pl.value_mem = reinterpret_cast<unsigned char*>(base) + kStaticScanHeader + flag_bytes;
     scan_lookback_kernel<T, OP><<<(unsigned)pl.ntiles, kScanThreads, 0, st->s>>>(
         (const T*)A, (T*)B, pl, reinterpret_cast<unsigned char*>(base) + kStaticScanHeader,
         reinterpret_cast<unsigned int*>(base), device_error_word(st->dev));
@@ -1058,7 +1087,7 @@ extern "C" int32_t b200_selftest_wait_timeout(b200_stream_t st, uint32_t polls) 
     void* scr = nullptr;
     unsigned int* counters = nullptr;
     const size_t data_bytes = 2 * (size_t)TILE * sizeof(int32_t);
-    const size_t sbytes = 256 + TileState<int32_t>::bytes(2) + 2 * data_bytes;
+    const size_t sbytes = 256 + TileState<int32_t>::flag_bytes(2) + 2 * data_bytes;   // cleared below: launch number 0
     B200_TRY(scratch(st, sbytes, &scr, &counters));
     B200_CUDA(cudaMemsetAsync(scr, 0, sbytes, st->s));
     unsigned char* base = reinterpret_cast<unsigned char*>(scr);

@@ -1,5 +1,5 @@
-// Definitions shared by the scan kernels (accumulate.cu, accumulate_ring.cu): operator algebra,
-// accumulator types, the plan a launch is described by, and the warp scan.
+// Definitions the scan kernels (accumulate.cu) share: operator algebra, accumulator types, the
+// plan a launch is described by, and the warp scan.
 #pragma once
 #include "program.cuh"
 
@@ -51,6 +51,8 @@ struct ScanPlan {
     uint32_t max_polls;
     uint64_t init;           // accumulator class bits (has_init == 1)
     const void* init_dev;    // one element of the array's type in device memory (has_init == 2)
+    uint32_t epoch;          // tag of this launch in the descriptor words (0: the words were cleared)
+    void* value_mem;         // 8-byte accumulators: aggregate / prefix values beside the flag words
 };
 
 template <typename T>
@@ -71,10 +73,5 @@ __device__ __forceinline__ Acc warp_scan_inclusive(Acc v, int lane) {
     return v;
 }
 
-
-// One-pass ring scan for long dense vectors (accumulate_ring.cu).  Returns B200_UNSUPPORTED when
-// the element type or the layout is outside what that kernel takes; the caller then uses the
-// two-pass segment kernel.
-int32_t launch_scan_ring(b200_stream_t st, int32_t dtype, int32_t op, const void* A, void* B, const ScanPlan& pl);
 
 }  // namespace b200

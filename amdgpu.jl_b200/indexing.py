@@ -61,6 +61,37 @@ def getindex_mask(xs: ROCArray, bools: ROCArray, stream: Stream | None = None) -
     return ys
 
 
+def getindex_mask_dim(xs: ROCArray, bools: ROCArray, dim: int, stream: Stream | None = None) -> ROCArray:
+    """``xs[:, ..., bools, ..., :]``: a Bool vector selects along dimension `dim` (1-based), colons
+    everywhere else (test/hip_rocarray/indexing.jl:9-18: ``xd[:, md]``, ``xd[:, :, md]``).  The kept
+    positions come from ``findall`` (a scan + compaction); the linear indices of all selected
+    elements are then formed by one fused broadcast over (leading, selected, trailing) and read
+    with the gather kernel - everything stays on the device except the count ``findall`` reads."""
+    if not 1 <= dim <= xs.ndim:
+        raise IndexError(f"dimension {dim} out of range for an array with {xs.ndim} dimensions")
+    if bools.ndim != 1 or bools.size != xs.dims[dim - 1]:
+        raise IndexError("the mask must be a vector as long as the dimension it selects from")
+    st = stream or current_stream()
+    keep = findall(bools, st)                              # 1-based positions along `dim`
+    k = keep.size
+    lead = int(np.prod(xs.dims[:dim - 1], dtype=np.int64))
+    extent = xs.dims[dim - 1]
+    trail = int(np.prod(xs.dims[dim:], dtype=np.int64))
+    out_dims = xs.dims[:dim - 1] + (k,) + xs.dims[dim:]
+    if k == 0 or lead == 0 or trail == 0:
+        return ROCArray(xs.dtype, out_dims, stream=st)
+    def iota(n):                                           # 1, 2, ..., n as Int64 on the device
+        return accumulate_("+", ROCArray(np.int64, (n,), stream=st), ROCArray(np.int64, (n,), stream=st).fill_(1, st), init=None, stream=st)
+    a = iota(lead).reshape(lead, 1, 1)
+    j = keep.reshape(1, k, 1)
+    m = iota(trail).reshape(1, 1, trail)
+    # 1-based linear index of element (a, j, m):  a + lead*(j-1) + lead*extent*(m-1)
+    expr = a.dot + (j.dot - 1) * lead + (m.dot - 1) * (lead * extent)
+    idx = expr.materialize(st)
+    xd = xs if xs.is_contiguous else xs.copy(st)
+    return getindex(xd, idx.reshape(idx.size), st).reshape(out_dims)
+
+
 def getindex(xs: ROCArray, ix: ROCArray, stream: Stream | None = None) -> ROCArray:
     """``xs[ix]`` with a device vector of 1-based integer indices (the vectorised ``getindex`` the
     reference's sorting tests use, test/hip_rocarray/sorting.jl:14).  `xs` is indexed linearly;

@@ -21,3 +21,25 @@ def assert_close(got, ref64, rtol, what="", atol=1e-30):
 def bits_equal(a, b):
     a, b = np.asarray(a), np.asarray(b)
     return a.dtype == b.dtype and a.shape == b.shape and a.tobytes() == b.tobytes()
+
+
+class Guarded:
+    """A destination array with guard bands: the array is a view into a larger buffer whose 4 KiB
+    before and after it hold a known byte pattern.  `check()` verifies that an operator wrote
+    nothing outside its destination - the stand-in for a memory checker on the device."""
+    BAND = 4096
+    PATTERN = 0xA5
+
+    def __init__(self, gpu, dtype, dims, misalign: int = 0):
+        dtype = np.dtype(dtype)
+        n = int(np.prod(dims, dtype=np.int64)) if not isinstance(dims, (int, np.integer)) else int(dims)
+        self.gpu, self.nbytes = gpu, n * dtype.itemsize
+        pad = misalign * dtype.itemsize                       # start the array off a 16-byte boundary
+        self.raw = gpu.ROCArray(np.uint8, self.BAND + pad + self.nbytes + self.BAND).fill_(self.PATTERN)
+        self.lo = self.BAND + pad
+        self.array = self.raw.view(self.lo, self.lo + self.nbytes).reinterpret(dtype).reshape(dims)
+
+    def check(self, what=""):
+        h = self.raw.to_host()
+        assert (h[:self.lo] == self.PATTERN).all(), (what, "wrote before its destination")
+        assert (h[self.lo + self.nbytes:] == self.PATTERN).all(), (what, "wrote past its destination")

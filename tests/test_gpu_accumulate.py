@@ -176,8 +176,10 @@ def test_ring_kernel_variants(gpu, orc):
     wd = gpu.ROCArray.from_host(w)
     assert np.array_equal(gpu.accumulate("max", wd, init=None).to_host(), np.maximum.accumulate(w))
     assert np.array_equal(gpu.accumulate("min", wd, init=np.float32(0.5)).to_host(), np.minimum.accumulate(np.minimum(w, 0.5)))
-    g = (1.0 + 1e-3 * (rng.random(n) - 0.5)).astype(np.float32)      # factors without rounding ties
-    assert_close(gpu.cumprod(gpu.ROCArray.from_host(g)).to_host(), np.cumprod(g.astype(np.float64)), 2e-4)
+    # factors spread over a binade (no rounding ties); products of two million Float32 factors
+    # carry the rounding of a tree of that depth, hence the wider tolerance
+    g = np.exp(rng.uniform(-0.01, 0.01, n)).astype(np.float32)
+    assert_close(gpu.cumprod(gpu.ROCArray.from_host(g)).to_host(), np.cumprod(g.astype(np.float64)), 5e-4)
     f = rng.random(n).astype(np.float32)
     assert_close(gpu.cumsum(gpu.ROCArray.from_host(f)).to_host(), np.cumsum(f.astype(np.float64)), 1e-5)
     h = np.where(np.arange(n) % 2 == 0, 1.0, -1.0).astype(np.float16)

@@ -64,3 +64,19 @@ def test_compaction_checks_its_positions(gpu):
         gpu.synchronize()
     assert np.array_equal(full.to_host(), [-7, 6, -7, -7])
     assert np.array_equal(gpu.findall(md).to_host(), [1, 3, 4, 6])
+
+
+def test_mask_along_one_dimension(gpu):
+    """xd[:, md] and xd[:, :, md] (test/hip_rocarray/indexing.jl:9-18), plus a mask in the middle."""
+    rng = np.random.default_rng(2)
+    for shape, dim in (((1, 16), 2), ((3, 1, 16), 3), ((5, 300), 2), ((40, 7, 9), 2), ((33, 4), 1), ((6,), 1)):
+        x = rng.integers(-1000, 1000, shape).astype(np.int32)
+        m = rng.random(shape[dim - 1]) < 0.5
+        xd, md = gpu.ROCArray.from_host(x), gpu.ROCArray.from_host(m)
+        want = np.compress(m, x, axis=dim - 1)
+        got = gpu.getindex_mask_dim(xd, md, dim)
+        assert got.dims == want.shape and np.array_equal(got.to_host(), want), (shape, dim)
+    none = gpu.getindex_mask_dim(gpu.ROCArray.from_host(np.ones((3, 4), np.float32)), gpu.ROCArray.from_host(np.zeros(4, bool)), 2)
+    assert none.dims == (3, 0)
+    with pytest.raises(IndexError):
+        gpu.getindex_mask_dim(gpu.ROCArray(np.float32, (3, 4)), gpu.ROCArray.from_host(np.zeros(3, bool)), 2)

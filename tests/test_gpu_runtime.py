@@ -64,7 +64,10 @@ def test_pool_accounting_and_limits(gpu):
     assert s2["free_count"] == s0["free_count"] + 1 and s2["live_bytes"] == s0["live_bytes"]
     with pytest.raises(RuntimeError):
         x.ptr
-    # out-of-memory injected through the host-side budget: nothing on the GPU faults
+    # out-of-memory injected through the host-side budget: nothing on the GPU faults.  (The retry
+    # ladder ends with reclaim, which also hands back operator scratch: do that first, so that the
+    # limit is set against what the arrays themselves hold.)
+    gpu.reclaim()
     live = gpu.pool_stats()["live_bytes"]
     gpu.configure(hard=f"{(live >> 20) + 64} MiB")
     try:
