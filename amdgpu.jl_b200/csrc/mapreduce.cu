@@ -636,11 +636,17 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
     if (fast) {
         int i0 = -1, i1 = -1;
         for (int d = 0; d < ndim; ++d) if (((mask >> d) & 1u) && shape[d] > 1) { if (i0 < 0) i0 = d; i1 = d; }
-        for (int d = i0; d <= i1 && fast; ++d) if (shape[d] > 1 && !((mask >> d) & 1u)) fast = false;
-        if (fast) {
-            for (int d = 0; d < i0; ++d) K *= shape[d];
-            for (int d = i0; d <= i1; ++d) L *= shape[d];
-            for (int d = i1 + 1; d < ndim; ++d) M *= shape[d];
+        if (i0 < 0) {
+            // no reduced dimension longer than one element (a one-element shard of a sharded
+            // reduction): every element is its own run
+            M = n;
+        } else {
+            for (int d = i0; d <= i1 && fast; ++d) if (shape[d] > 1 && !((mask >> d) & 1u)) fast = false;
+            if (fast) {
+                for (int d = 0; d < i0; ++d) K *= shape[d];
+                for (int d = i0; d <= i1; ++d) L *= shape[d];
+                for (int d = i1 + 1; d < ndim; ++d) M *= shape[d];
+            }
         }
     }
     if (fast && n == 0) {

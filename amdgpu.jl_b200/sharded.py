@@ -233,7 +233,7 @@ def prepared_mapreduce_allreduce(peer, expr, op, R, init, stream):
 
 
 _TRANSPORTS = {"host": 0, "vmm": 1, "ipc": 2}
-DEFAULT_TRANSPORT = "host"
+DEFAULT_TRANSPORT = "vmm"
 
 
 def _pass_descriptors(rank: int, world: int, handle: bytes, allgather) -> bytes:
@@ -290,30 +290,65 @@ def _pass_descriptors(rank: int, world: int, handle: bytes, allgather) -> bytes:
 
 def init_peer(rank: int, world: int, device: int, allgather, transport: str | None = None) -> C.c_void_p:
     """Creates this rank's peer-exchange group.  `allgather(obj) -> list` must return every
-    rank's argument in rank order on every rank (any host channel).  `transport` is "host"
-    (slots in shared host memory, no GPU maps another GPU), "vmm" (one exported device
-    allocation per rank, mapped by the peers over NVLink) or "ipc" (CUDA IPC, enables peer
-    access device wide); default: environment B200_PEER_TRANSPORT, else "host"."""
+    rank's argument in rank order on every rank (any host channel).  `transport` is "vmm" (one
+    exported device allocation per rank, mapped by the peers over NVLink; peer access for that
+    allocation only), "host" (slots in shared host memory, no GPU maps another GPU) or "ipc" (CUDA
+    IPC, enables peer access device wide).  Default: environment B200_PEER_TRANSPORT, else "vmm"
+    with "host" as the fallback when any rank cannot export or map device memory - the ranks
+    agree on that over `allgather`, so they always end up on the same transport."""
+    from . import _lib
     from ._lib import check, lib
-    name = (transport or os.environ.get("B200_PEER_TRANSPORT") or DEFAULT_TRANSPORT).lower()
+    name = (transport or os.environ.get("B200_PEER_TRANSPORT") or "").lower()
+    fallback = name == ""
+    name = name or DEFAULT_TRANSPORT
     if name not in _TRANSPORTS:
         raise ValueError(f"unknown peer transport {name!r}: use one of {sorted(_TRANSPORTS)}")
-    peer = C.c_void_p()
-    buf = C.create_string_buffer(64)
-    check(lib.b200_peer_create(device, rank, world, _TRANSPORTS[name], C.byref(peer), buf))
-    if world == 1:
-        return peer
-    if name == "vmm":
-        handles = _pass_descriptors(rank, world, buf.raw, allgather)
+
+    def agree(ok: bool) -> bool:
+        """True when the step worked on every rank (one exchange over the host channel)."""
+        return all(allgather(bool(ok))) if world > 1 else bool(ok)
+
+    def attempt(kind: str):
+        """Create, then connect; after each step the ranks agree on whether all of them got through,
+        so that either every rank holds a connected group or none does."""
+        peer = C.c_void_p()
+        buf = C.create_string_buffer(64)
+        status = lib.b200_peer_create(device, rank, world, _TRANSPORTS[kind], C.byref(peer), buf)
+        msg = "" if status == _lib.OK else _lib.last_error()
+        if not agree(status == _lib.OK):
+            if status == _lib.OK:
+                lib.b200_peer_destroy(peer)
+                status, msg = _lib.UNSUPPORTED, f"another rank could not create a {kind} exchange buffer"
+            return None, status, msg
+        if world == 1:
+            return peer, _lib.OK, ""
         try:
-            check(lib.b200_peer_connect(peer, handles))
-        finally:
-            import struct
-            for r in range(world):          # the library duplicated what it needed
-                if r != rank:
-                    os.close(struct.unpack_from("<IiiiQ", handles, 64 * r)[2])
-    else:
-        check(lib.b200_peer_connect(peer, b"".join(allgather(buf.raw))))
+            if kind == "vmm":
+                handles = _pass_descriptors(rank, world, buf.raw, allgather)
+                try:
+                    status = lib.b200_peer_connect(peer, handles)
+                finally:
+                    import struct
+                    for r in range(world):          # the library duplicated what it needed
+                        if r != rank:
+                            os.close(struct.unpack_from("<IiiiQ", handles, 64 * r)[2])
+            else:
+                status = lib.b200_peer_connect(peer, b"".join(allgather(buf.raw)))
+            msg = "" if status == _lib.OK else _lib.last_error()
+        except OSError as e:                          # descriptor passing failed on this rank
+            status, msg = _lib.UNSUPPORTED, str(e)
+        if not agree(status == _lib.OK):
+            lib.b200_peer_destroy(peer)
+            if status == _lib.OK:
+                status, msg = _lib.UNSUPPORTED, f"another rank could not map the {kind} exchange buffers"
+            return None, status, msg
+        return peer, _lib.OK, ""
+
+    peer, status, msg = attempt(name)
+    if peer is None and fallback and name != "host":
+        peer, status, msg = attempt("host")
+    if peer is None:
+        raise _lib.B200Error(status, msg)
     return peer
 
 

@@ -13,6 +13,8 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def _setup(rank, world, port):
+    import faulthandler
+    faulthandler.enable()                     # a crash in native code names the Python line it came from
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist

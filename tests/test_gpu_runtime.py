@@ -165,4 +165,4 @@ def test_reclaim_returns_operator_scratch(gpu):
     assert gpu.pool_stats()["live_bytes"] == base
     # scratch comes back on demand
     x = gpu.ROCArray.from_host(np.arange(1 << 21, dtype=np.int32))
-    assert int(gpu.cumsum(x).to_host()[-1]) == (1 << 21) * ((1 << 21) - 1) // 2
+    assert int(gpu.cumsum(x).to_host()[-1]) == int(np.int64((1 << 21) * ((1 << 21) - 1) // 2).astype(np.int32))   # Int32 wraps
