@@ -431,7 +431,7 @@ __device__ __forceinline__ void strided_body(const Tin* A, const StridedPlan& pl
 }
 
 template <typename Tin, typename Acc, int V>
-__global__ void __launch_bounds__(kRedThreads)
+__global__ void __launch_bounds__(kRedThreads, V >= 8 ? 5 : 1)
 reduce_strided_kernel(const Tin* A, StridedPlan pl, int mapop, Acc* partials, unsigned int* counters, RedOut out) {
     __shared__ Acc smem[kRedThreads * V];
 #define CALL(MAPV, OPV) strided_body<Tin, Acc, MAPV, OPV, V>(A, pl, partials, counters, out, smem)
