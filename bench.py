@@ -315,6 +315,42 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
             out["c4_sort_2p28_u32"] = {"ms": round(ms, 3), "Gkeys/s": round(n / ms / 1e6, 2), "model_GB/s": round(36 * n / ms / 1e6, 1),
                                        "frac_of_8TBs_model36B": round(36 * n / ms / 1e6 / NOMINAL_HBM_GBS, 3)}
         del v, o
+    # yardsticks only: the vendor library kernels torch ships (CUB scan / radix sort, its own
+    # reductions) on the same sizes, timed the same way on torch's stream.  Not part of any path
+    # of this library; they say what "good" is on this box.
+    if want("yardstick"):
+        try:
+            import torch
+            dev = torch.device("cuda", pkg.current_device())
+            def ttime(fn, reps_):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize(dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps_):
+                    fn()
+                e1.record()
+                e1.synchronize()
+                return e0.elapsed_time(e1) / reps_
+            with torch.cuda.device(dev):
+                n28 = (1 << 28) >> shrink
+                xi = torch.randint(-100, 101, (n28,), dtype=torch.int32, device=dev)
+                ms = ttime(lambda: torch.cumsum(xi, 0, dtype=torch.int32), reps(10))
+                out["yardstick_torch_cumsum_2p28_i32"] = {"ms": round(ms, 4), "GB/s": round(8 * n28 / ms / 1e6, 1)}
+                xf = torch.rand(n28, dtype=torch.float32, device=dev)
+                ms = ttime(lambda: torch.sum(xf), reps(10))
+                out["yardstick_torch_sum_2p28_f32"] = {"ms": round(ms, 4), "GB/s": round(4 * n28 / ms / 1e6, 1)}
+                ms = ttime(lambda: torch.cumsum(xf, 0), reps(10))
+                out["yardstick_torch_cumsum_2p28_f32"] = {"ms": round(ms, 4), "GB/s": round(8 * n28 / ms / 1e6, 1)}
+                del xf
+                keys = xi.view(torch.int32)
+                ms = ttime(lambda: torch.sort(keys), reps(3))
+                out["yardstick_torch_sort_2p28_i32(keys+indices)"] = {"ms": round(ms, 3), "Gkeys/s": round(n28 / ms / 1e6, 2)}
+                del xi, keys
+                torch.cuda.empty_cache()
+        except Exception as e:                      # no torch CUDA build on this box: no yardstick
+            out["yardstick_torch"] = {"unavailable": str(e)[:200]}
     if want("c4_sortperm"):
         m2 = (1 << 26) >> shrink
         f = R.fill_random_(pkg.ROCArray(np.float32, m2), R.NORMAL_DUP1PCT, seed=3, hi=m2)
