@@ -9,7 +9,7 @@ from helpers import assert_close, bits_equal
 pytestmark = pytest.mark.gpu
 G = np.load(Path(__file__).parent / "golden" / "known_answers.npz")
 NS = (0, 1, 2, 3, 10, 10_000, 16384, 16384 + 1, 4095, 4096, 4097, 8192 * 3 - 1, 1_000_003,
-      1 << 20, (1 << 21) + 32, 3 * (1 << 19) + 4, 5_000_000)     # the last four take the persistent ring kernel
+      1 << 20, (1 << 21) + 32, 3 * (1 << 19) + 4, 5_000_000)     # the last four take the persistent segment kernel
 
 
 def test_golden(gpu):
@@ -156,12 +156,12 @@ def test_scans_down_a_strided_dimension(gpu, orc, sizes):
     assert_close(dst.to_host(), orc.accumulate("+", src.to_host(), axis=1), 1e-5)
 
 
-def test_ring_kernel_variants(gpu, orc):
-    """The one-pass kernel for long dense vectors: in place, exclusive, seeded, max/min/prod, 16-bit
-    elements, a last tile of every fill level, many launches in a row (descriptor tags, alternating
-    ticket words) and a captured launch that is replayed."""
+def test_long_vector_scan_forms(gpu, orc):
+    """The persistent kernel for long dense vectors: in place, exclusive, seeded, max/min/prod, 16-bit
+    elements, a last segment of every fill level, many launches in a row (descriptor words tagged
+    with the launch number, never cleared in between) and a captured launch that is replayed."""
     rng = np.random.default_rng(9)
-    tile = 8192                                   # Float32 elements per tile of the ring kernel
+    tile = 8192                                   # sizes around multiples of 148 blocks x 8192 elements
     for n in (1 << 18, (1 << 18) + 4, 5 * tile - 4, 148 * tile, 149 * tile + 2044, 3 * 148 * tile + 12, (1 << 24) + 8):
         x = rng.integers(-100, 101, n).astype(np.int32)
         xd = gpu.ROCArray.from_host(x)
