@@ -160,6 +160,7 @@ SIGNATURES = {
     "b200_selftest_wait_timeout": [_vp, C.c_uint32],
     "b200_peer_create": [_i32, _i32, _i32, _i32, _P(_vp), C.c_char_p],
     "b200_peer_connect": [_vp, C.c_char_p],
+    "b200_peer_seal": [_vp],
     "b200_peer_set_poll_budget": [_vp, C.c_uint32],
     "b200_peer_info": [_vp, _P(_i32), _P(_u64)],
     "b200_peer_destroy": [_vp],

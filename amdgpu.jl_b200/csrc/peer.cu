@@ -332,6 +332,22 @@ extern "C" int32_t b200_peer_info(b200_peer_t p, int32_t* transport, uint64_t* s
     return B200_OK;
 }
 
+// Every rank has mapped every buffer: the names the mappings were found by are not needed any
+// more.  Removing them now means a process that dies later leaves no file in /dev/shm and no open
+// descriptor behind; the mappings themselves live until b200_peer_destroy.
+extern "C" int32_t b200_peer_seal(b200_peer_t p) {
+    if (!p) return fail(B200_INVALID_ARG, "null peer group");
+    if (p->transport == B200_PEER_HOST && p->shm_name[0]) {
+        shm_unlink(p->shm_name);
+        p->shm_name[0] = 0;
+    }
+    if (p->export_fd >= 0) {
+        close(p->export_fd);
+        p->export_fd = -1;
+    }
+    return B200_OK;
+}
+
 extern "C" int32_t b200_peer_destroy(b200_peer_t p) {
     if (!p) return B200_OK;
     cudaSetDevice(p->dev);

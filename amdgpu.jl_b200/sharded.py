@@ -342,6 +342,7 @@ def init_peer(rank: int, world: int, device: int, allgather, transport: str | No
             if status == _lib.OK:
                 status, msg = _lib.UNSUPPORTED, f"another rank could not map the {kind} exchange buffers"
             return None, status, msg
+        lib.b200_peer_seal(peer)        # everyone holds its mappings: drop the names they were found by
         return peer, _lib.OK, ""
 
     peer, status, msg = attempt(name)

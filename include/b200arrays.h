@@ -342,6 +342,11 @@ enum { B200_PEER_HOST = 0, B200_PEER_VMM = 1, B200_PEER_IPC = 2 };
 int32_t b200_peer_create(int32_t dev, int32_t rank, int32_t nranks, int32_t transport, b200_peer_t* out,
                          uint8_t handle_out[64]);
 int32_t b200_peer_connect(b200_peer_t peer, const uint8_t* handles);
+/* Call once EVERY rank's b200_peer_connect has returned (the caller knows: one round over its host
+ * channel): removes the shared-memory name / closes the exported descriptor, so a process that
+ * dies later leaves nothing behind.  Optional; b200_peer_destroy does the same.  No counterpart in
+ * the reference. */
+int32_t b200_peer_seal(b200_peer_t peer);
 /* how often the exchange polls for a peer's partial before it gives up and latches
  * B200_LOOKBACK_TIMEOUT (default 2^26, about ten seconds with the back-off) */
 int32_t b200_peer_set_poll_budget(b200_peer_t peer, uint32_t polls);
