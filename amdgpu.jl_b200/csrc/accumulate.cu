@@ -349,6 +349,8 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
     __shared__ int s_wflag[kSegWarps];
     __shared__ int s_verdict, s_abort;
 
+    grid_dependency_wait();
+    grid_dependency_release();
     TileState<Acc> state;
     state.bind(state_mem, pl.value_mem, pl.nsegs, pl.epoch);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -860,7 +862,8 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         void* scr = nullptr;
         B200_TRY(descriptor_storage<Acc>(st, sp.nsegs, &scr, &sp.value_mem, &sp.epoch));
         if (grid > sp.nsegs) grid = sp.nsegs;
-        scan_segment_kernel<T, OP><<<(unsigned)grid, kSegThreads, 0, st->s>>>((const T*)A, (T*)B, sp, scr, device_error_word(st->dev));
+        launch_overlapped(scan_segment_kernel<T, OP>, (unsigned)grid, kSegThreads, 0, st->s,
+                          (const T*)A, (T*)B, sp, scr, device_error_word(st->dev));
         return B200_OK;
     }
     pl.tiles_per_col = (pl.L + TILE - 1) / TILE;

@@ -392,6 +392,8 @@ ew_stream_kernel(T* out, const T* in0, const T* in1, const T* in2, F f, int64_t 
     constexpr int64_t TILE = (int64_t)kEwThreads * kEwUnroll * V;
     const int64_t ntiles = (n + TILE - 1) / TILE;
     using VT = Vec<T, V>;
+    grid_dependency_wait();
+    grid_dependency_release();
     for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
         const int64_t base = tile * TILE;
         if (vec_ok && base + TILE <= n) {
@@ -433,11 +435,15 @@ static void launch_stream(b200_stream_t st, void* out, const void* a, const void
     constexpr int V = 16 / sizeof(T);
     const int64_t TILE = (int64_t)kEwThreads * kEwUnroll * V;
     const int64_t tiles = (n + TILE - 1) / TILE;
-    const unsigned grid = balanced_grid(tiles, resident_blocks(ew_stream_kernel<T, F, NIN>, kEwThreads, 0, st->dev));
+    // One tile per block and the hardware block scheduler, not a persistent wave: blocks that
+    // start as others retire spread reads and writes evenly over time, where a resident wave moves
+    // in lock step (all loading, then all storing).  Measured on B200: 30.9 us against 34.7 us at
+    // 2^24 Float32 (axpy), 2.40 ms against 2.49 ms at 2^30 (three inputs).
+    const unsigned grid = (unsigned)(tiles < 1 ? 1 : (tiles > 0x7fffffff ? 0x7fffffff : tiles));
     auto al = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     int vec_ok = al(out) && al(a) && al(b) && al(c);
-    ew_stream_kernel<T, F, NIN><<<grid, kEwThreads, 0, st->s>>>(
-        (T*)out, (const T*)a, (const T*)b, (const T*)c, f, n, vec_ok);
+    launch_overlapped(ew_stream_kernel<T, F, NIN>, grid, kEwThreads, 0, st->s,
+                      (T*)out, (const T*)a, (const T*)b, (const T*)c, f, n, vec_ok);
 }
 
 // ---- host: pattern matching on the compiled program ----------------------------------------------------

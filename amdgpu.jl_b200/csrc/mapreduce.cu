@@ -262,6 +262,8 @@ template <typename Tin, typename Acc>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_contig_block_kernel(const Tin* A, int64_t L, int64_t M, int B, int64_t chunk, int mapop,
                            Acc* partials, unsigned int* counters, RedOut out, const __grid_constant__ PeerCtx peer) {
+    grid_dependency_wait();
+    grid_dependency_release();
 #define CALL(MAPV, OPV) contig_block_body<Tin, Acc, MAPV, OPV>(A, L, M, B, chunk, partials, counters, out, peer)
     B200_MAPOP_SWITCH(mapop, CALL)
 #undef CALL
@@ -285,6 +287,8 @@ __device__ __forceinline__ void contig_warp_body(const Tin* A, int64_t L, int64_
 template <typename Tin, typename Acc>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_contig_warp_kernel(const Tin* A, int64_t L, int64_t M, int mapop, RedOut out) {
+    grid_dependency_wait();
+    grid_dependency_release();
 #define CALL(MAPV, OPV) contig_warp_body<Tin, Acc, MAPV, OPV>(A, L, M, out)
     B200_MAPOP_SWITCH(mapop, CALL)
 #undef CALL
@@ -304,6 +308,8 @@ __device__ __forceinline__ void contig_thread_body(const Tin* A, int64_t L, int6
 template <typename Tin, typename Acc>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_contig_thread_kernel(const Tin* A, int64_t L, int64_t M, int mapop, RedOut out) {
+    grid_dependency_wait();
+    grid_dependency_release();
 #define CALL(MAPV, OPV) contig_thread_body<Tin, Acc, MAPV, OPV>(A, L, M, out)
     B200_MAPOP_SWITCH(mapop, CALL)
 #undef CALL
@@ -434,6 +440,8 @@ template <typename Tin, typename Acc, int V>
 __global__ void __launch_bounds__(kRedThreads, V >= 8 ? 5 : 1)
 reduce_strided_kernel(const Tin* A, StridedPlan pl, int mapop, Acc* partials, unsigned int* counters, RedOut out) {
     __shared__ Acc smem[kRedThreads * V];
+    grid_dependency_wait();
+    grid_dependency_release();
 #define CALL(MAPV, OPV) strided_body<Tin, Acc, MAPV, OPV, V>(A, pl, partials, counters, out, smem)
     B200_MAPOP_SWITCH(mapop, CALL)
 #undef CALL
@@ -486,12 +494,14 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
     if (K == 1) {
         if (!peer && M > 1 && L <= 16) {
             const int64_t res = resident_blocks(reduce_contig_thread_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
-            reduce_contig_thread_kernel<Tin, Acc><<<balanced_grid((M + kRedThreads - 1) / kRedThreads, res), kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
+            launch_overlapped(reduce_contig_thread_kernel<Tin, Acc>, balanced_grid((M + kRedThreads - 1) / kRedThreads, res), kRedThreads, 0, st->s,
+                              (const Tin*)A, L, M, mapop, out);
             return B200_OK;
         }
         const int64_t wres = resident_blocks(reduce_contig_warp_kernel<Tin, Acc>, kRedThreads, 0, st->dev);
         if (!peer && M >= wres * 8 && (size_t)L * sizeof(Tin) <= 65536) {
-            reduce_contig_warp_kernel<Tin, Acc><<<balanced_grid((M + 7) / 8, wres), kRedThreads, 0, st->s>>>((const Tin*)A, L, M, mapop, out);
+            launch_overlapped(reduce_contig_warp_kernel<Tin, Acc>, balanced_grid((M + 7) / 8, wres), kRedThreads, 0, st->s,
+                              (const Tin*)A, L, M, mapop, out);
             return B200_OK;
         }
         // the grid is exactly one resident wave: blocks per column fill it, each block with at
@@ -510,8 +520,8 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
         B200_TRY(scratch(st, (size_t)(M * B) * sizeof(Acc), &scr, &counters));
         // the collective's sequence number is taken last: a call that fails above must not count
         if (peer) B200_TRY(peer_next_context(peer, st, &pc));
-        reduce_contig_block_kernel<Tin, Acc><<<balanced_grid(M * B, target), kRedThreads, 0, st->s>>>(
-            (const Tin*)A, L, M, (int)B, chunk, mapop, (Acc*)scr, counters, out, pc);
+        launch_overlapped(reduce_contig_block_kernel<Tin, Acc>, balanced_grid(M * B, target), kRedThreads, 0, st->s,
+                          (const Tin*)A, L, M, (int)B, chunk, mapop, (Acc*)scr, counters, out, pc);
         return B200_OK;
     }
     // strided
@@ -540,8 +550,8 @@ static int32_t launch_fast(b200_stream_t st, const void* A, int64_t K, int64_t L
     pl.nstrips = (int)((L + pl.LS - 1) / pl.LS);
     B200_TRY(scratch(st, (size_t)(base_blocks * pl.nstrips * pl.kx * V) * sizeof(Acc), &scr, &counters));
     const unsigned blocks = balanced_grid(base_blocks * pl.nstrips, target);
-    if (vec) reduce_strided_kernel<Tin, Acc, VMAX><<<blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
-    else reduce_strided_kernel<Tin, Acc, 1><<<blocks, kRedThreads, 0, st->s>>>((const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
+    if (vec) launch_overlapped(reduce_strided_kernel<Tin, Acc, VMAX>, (unsigned)blocks, kRedThreads, 0, st->s, (const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
+    else launch_overlapped(reduce_strided_kernel<Tin, Acc, 1>, (unsigned)blocks, kRedThreads, 0, st->s, (const Tin*)A, pl, mapop, (Acc*)scr, counters, out);
     return B200_OK;
 }
 
@@ -722,7 +732,7 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
     const unsigned blocks = balanced_grid(n_out * B, target);
     if (special) {
         void* args[] = {(void*)&C.P, (void*)&O, (void*)&G, (void*)&scr, (void*)&counters, (void*)&out};
-        if (cudaLaunchKernel(special, dim3(blocks), dim3(kRedThreads), args, 0, st->s) == cudaSuccess)
+        if (launch_overlapped_handle(special, blocks, kRedThreads, args, st->s) == cudaSuccess)
             return finish(st, "b200_mapreduce");
         cudaGetLastError();      // fall through to the interpreter
     }

@@ -38,6 +38,14 @@ int32_t fail(int32_t code, const char* fmt, ...) {
     return code;
 }
 
+bool overlap_launches_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("B200_OVERLAP_LAUNCHES");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 void log_debug(const char* fmt, ...) {
     if (log_level() < 2) return;
     char buf[512];

@@ -348,6 +348,26 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
                 ms = ttime(lambda: torch.sort(keys), reps(3))
                 out["yardstick_torch_sort_2p28_i32(keys+indices)"] = {"ms": round(ms, 3), "Gkeys/s": round(n28 / ms / 1e6, 2)}
                 del xi, keys
+                # the 2^24 cases, rotating over four buffer sets like the c1 cases above
+                n24 = (1 << 24) >> shrink
+                sets24 = [(torch.rand(n24, dtype=torch.float32, device=dev), torch.rand(n24, dtype=torch.float32, device=dev),
+                           torch.empty(n24, dtype=torch.float32, device=dev)) for _ in range(4)]
+                k = [0]
+                def nxt():
+                    k[0] += 1
+                    return sets24[k[0] % 4]
+                def t_axpy():
+                    x_, y_, z_ = nxt()
+                    torch.add(y_, x_, alpha=2.5, out=z_)
+                def t_sum():
+                    torch.sum(nxt()[0])
+                def t_cumsum():
+                    x_, _, z_ = nxt()
+                    torch.cumsum(x_, 0, out=z_)
+                for name, fn_, nb in (("axpy", t_axpy, 12), ("sum", t_sum, 4), ("cumsum", t_cumsum, 8)):
+                    ms = ttime(fn_, reps(200))
+                    out[f"yardstick_torch_{name}_2p24_f32"] = {"ms": round(ms, 4), "GB/s": round(nb * n24 / ms / 1e6, 1)}
+                del sets24
                 torch.cuda.empty_cache()
         except Exception as e:                      # no torch CUDA build on this box: no yardstick
             out["yardstick_torch"] = {"unavailable": str(e)[:200]}

@@ -166,3 +166,30 @@ def test_reclaim_returns_operator_scratch(gpu):
     # scratch comes back on demand
     x = gpu.ROCArray.from_host(np.arange(1 << 21, dtype=np.int32))
     assert int(gpu.cumsum(x).to_host()[-1]) == int(np.int64((1 << 21) * ((1 << 21) - 1) // 2).astype(np.int32))   # Int32 wraps
+
+
+def test_dependent_small_kernels_back_to_back(gpu):
+    """Kernels that may overlap the tail of their predecessor on the stream still see everything
+    it wrote: a long chain of small dependent operators (in-place update, scan of the result,
+    reduction of the scan) with no host synchronisation in between, checked exactly in Int32."""
+    rng = np.random.default_rng(5)
+    n = 1 << 19                                    # 2 MiB: the streaming, segment-scan and block-reduction kernels
+    x = rng.integers(-3, 4, n).astype(np.int32)
+    y = rng.integers(-3, 4, n).astype(np.int32)
+    xd, yd = gpu.ROCArray.from_host(x), gpu.ROCArray.from_host(y)
+    scan = gpu.ROCArray(np.int32, n)
+    tot = gpu.ROCArray(np.int32, 1)
+    totals = []
+    for k in range(60):
+        gpu.broadcast.materialize_(xd, xd.dot + yd.dot)            # x .+= y
+        gpu.accumulate_("+", scan, xd, init=None)
+        gpu.mapreducedim_("identity", "+", tot, scan, init=np.int32(0))
+        gpu.broadcast.materialize_(yd, yd.dot * np.int32(-1))      # y .= -y, read by the next round
+        totals.append(tot.copy())
+    ref_x, ref_y = x.copy(), y.copy()
+    for k in range(60):
+        ref_x = ref_x + ref_y
+        want = np.cumsum(ref_x, dtype=np.int32).sum(dtype=np.int32)
+        ref_y = -ref_y
+        assert int(totals[k].to_host()[0]) == int(want), k
+    assert np.array_equal(xd.to_host(), ref_x)
