@@ -53,7 +53,11 @@ template <> struct InClass<__half> { using type = float; };
 template <> struct InClass<__nv_bfloat16> { using type = float; };
 template <typename T> __device__ __forceinline__ typename InClass<T>::type widen(T v) { return v; }
 template <> __device__ __forceinline__ float widen<__half>(__half v) { return __half2float(v); }
-template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+// BFloat16 is the upper half of a binary32: widening is a shift (exact for every value, NaN
+// payloads included), which keeps the conversion pipe out of the inner loop
+template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) {
+    return __uint_as_float((uint32_t)__bfloat16_as_ushort(v) << 16);
+}
 
 // f is applied in the element's own arithmetic class, then the value widens to the accumulator.
 template <typename Tin, typename Acc, int MAP>

@@ -36,10 +36,10 @@ import __graft_entry__ as entry  # noqa: E402
 BYTES_PER_ELEM = 16 + 4          # broadcast: 3 reads + 1 write; reduction: 1 read
 # DRAM bytes per element of the broadcast kernel from its ncu capture on a 2^28-element launch
 # (dram__bytes_read.sum 3221.3 MB + dram__bytes_write.sum 1043.6 MB for 2^28 elements; the reads are
-# exactly the three inputs, 2.8 % of the output was still dirty in L2 when the kernel ended); traffic
+# exactly the three inputs, 2.7 % of the output was still dirty in L2 when the kernel ended); traffic
 # grows in proportion to the element count, so a launch over n elements moves this many bytes per
 # element.
-EW_TRAFFIC_BYTES_PER_ELEM = 4264.9e6 / (1 << 28)
+EW_TRAFFIC_BYTES_PER_ELEM = 4265.96e6 / (1 << 28)
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -725,7 +725,7 @@ def main():
                      "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 3),
                      "peak_source": f"{peak_kind} copy bandwidth", "traffic": round(EW_TRAFFIC_BYTES_PER_ELEM * n),
                      "traffic_source": "ncu capture of a 2^28-element launch (profiles/ew_stream_kernel_c5_2p28_traffic.md) scaled by the "
-                                       "element count; the reads are exactly the inputs, 2.8 % of the output was still dirty in L2 at the end",
+                                       "element count; the reads are exactly the inputs, 2.7 % of the output was still dirty in L2 at the end",
                      "ms_per_launch": round(ms_bc, 4), "ms_per_launch_over_ranks": spread("bc"), "algorithmic_bytes_per_launch": 16 * n,
                      "reduce_kernel": {"ms_per_launch": round(ms_red, 4), "achieved": round(4 * n / ms_red / 1e6, 1),
                                        "frac": round(4 * n / ms_red / 1e6 / peak, 3), "ms_per_launch_over_ranks": spread("red")},
