@@ -19,6 +19,7 @@ from . import broadcast
 from .broadcast import Broadcasted, materialize_, promote_type
 from .mapreduce import mapreducedim_, mapreduce, sum, prod, maximum, minimum   # noqa: A004
 from .mapreduce import prepared as mapreduce_prepared
+from .mapreduce import precompile as mapreduce_precompile
 from .accumulate import accumulate_, accumulate, cumsum, cumprod
 from .accumulate import prepared as accumulate_prepared
 from .sorting import sort_, sort, sortperm_, sortperm

@@ -140,6 +140,7 @@ SIGNATURES = {
     "b200_jit_configure": [_i32],
     "b200_jit_stats": [_P(C.c_uint64)],
     "b200_mapreduce": [_vp, _P(Tensor), _P(_i64), _i32, _P(Leaf), _i32, C.c_char_p, _i32, _i32, _vp],
+    "b200_mapreduce_prepare": [_P(Tensor), _P(_i64), _i32, _P(Leaf), _i32, C.c_char_p, _i32, _i32],
     "b200_accumulate": [_vp, _P(Tensor), _P(Tensor), _i32, _vp, _i32, _i32],
     "b200_accumulate_carry": [_vp, _P(Tensor), _P(Tensor), _i32, _vp, _i32, _i32],
     "b200_accumulate_noalloc": [_vp, _P(Tensor), _P(Tensor), _i32, _vp, _i32, _i32],

@@ -167,9 +167,20 @@ bool compile(const std::string& src, std::vector<char>* cubin) {
     nvrtcProgram prog = nullptr;
     if (g_nvrtc.CreateProgram(&prog, src.c_str(), "b200_jit.cu", 6, header_src, header_names) != NVRTC_SUCCESS) return false;
     std::string inc = std::string("-I") + (getenv("B200_CUDA_INCLUDE") ? getenv("B200_CUDA_INCLUDE") : "/usr/local/cuda/include");
-    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", inc.c_str()};
-    const nvrtcResult r = g_nvrtc.CompileProgram(prog, 4, opts);
+    // B200_LOG=debug: ptxas reports registers, spills and shared memory of every kernel it builds
+    static const bool verbose = [] { const char* e = getenv("B200_LOG"); return e && strcmp(e, "debug") == 0; }();
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", inc.c_str(), "--ptxas-options=-v"};
+    const nvrtcResult r = g_nvrtc.CompileProgram(prog, verbose ? 5 : 4, opts);
     bool ok = r == NVRTC_SUCCESS;
+    if (ok && verbose) {
+        size_t n = 0;
+        std::string log;
+        if (g_nvrtc.GetProgramLogSize(prog, &n) == NVRTC_SUCCESS && n > 1) {
+            log.resize(n);
+            g_nvrtc.GetProgramLog(prog, &log[0]);
+            log_debug("run-time compiler: %.480s", log.c_str());
+        }
+    }
     if (!ok) {
         size_t n = 0;
         if (g_nvrtc.GetProgramLogSize(prog, &n) == NVRTC_SUCCESS && n > 1) {
@@ -211,6 +222,15 @@ int32_t jit_prepare(const Compiled& C, int out_dtype) {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!enabled()) return fail(B200_UNSUPPORTED, "run-time specialisation is switched off");
     if (!lookup(C, out_dtype)) return fail(B200_UNSUPPORTED, "run-time specialisation failed: %.400s", g_last_log.c_str());
+    return B200_OK;
+}
+
+// The same for the kernel of a mapreduce over this map expression.
+int32_t jit_prepare_reduce(const Compiled& C, int out_dtype, int redop, int acc_dtype, int full) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!enabled()) return fail(B200_UNSUPPORTED, "run-time specialisation is switched off");
+    const ReduceInfo red{redop, acc_dtype, full};
+    if (!lookup(C, out_dtype, &red)) return fail(B200_UNSUPPORTED, "run-time specialisation failed: %.400s", g_last_log.c_str());
     return B200_OK;
 }
 

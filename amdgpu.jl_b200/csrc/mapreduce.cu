@@ -53,11 +53,7 @@ template <> struct InClass<__half> { using type = float; };
 template <> struct InClass<__nv_bfloat16> { using type = float; };
 template <typename T> __device__ __forceinline__ typename InClass<T>::type widen(T v) { return v; }
 template <> __device__ __forceinline__ float widen<__half>(__half v) { return __half2float(v); }
-// BFloat16 is the upper half of a binary32: widening is a shift (exact for every value, NaN
-// payloads included), which keeps the conversion pipe out of the inner loop
-template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) {
-    return __uint_as_float((uint32_t)__bfloat16_as_ushort(v) << 16);
-}
+template <> __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // f is applied in the element's own arithmetic class, then the value widens to the accumulator.
 template <typename Tin, typename Acc, int MAP>
@@ -591,9 +587,11 @@ static int32_t launch_peer_neutral(b200_stream_t st, b200_peer_t peer, int acc_d
 
 static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
                               const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
-                              int32_t ninstr, int32_t op, const void* init, b200_peer_t peer) {
-    B200_TRY(enter(st));
-    StreamGuard guard(st);
+                              int32_t ninstr, int32_t op, const void* init, b200_peer_t peer, bool prepare_only = false) {
+    // prepare_only: validate, and compile the kernel this call would need; no stream, no device
+    if (!prepare_only) B200_TRY(enter(st));
+    std::unique_lock<std::recursive_mutex> guard;
+    if (!prepare_only) guard = std::unique_lock<std::recursive_mutex>(st->mu);
     B200_TRY(check_tensor(R, "mapreduce destination"));
     if (!shape && ndim > 0) return fail(B200_INVALID_ARG, "mapreduce: null shape");
     if (ndim < 0 || ndim > B200_MAX_DIMS) return fail(B200_INVALID_ARG, "mapreduce: ndim %d outside [0,%d]", ndim, B200_MAX_DIMS);
@@ -663,6 +661,7 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
             }
         }
     }
+    if (prepare_only && fast) return B200_OK;     // served by a kernel that is part of the library
     if (fast && n == 0) {
         // empty shard of a sharded reduction; whether the expression is one the fused kernel
         // handles was decided above exactly as on the ranks that hold data
@@ -705,6 +704,7 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
     G.acc_dtype = acc_dt;
     G.identity = identity_bits(op, acc_dt);
     if (!G.full) { C.P.linear = 0; C.P.vec_ok = 0; }
+    if (prepare_only) return jit_prepare_reduce(C, R->dtype, op, acc_dt, G.full);
     // the kernel specialised for this expression at run time if there is one, else the interpreter
     LeafDesc O{};
     O.ptr = R->ptr;
@@ -749,6 +749,11 @@ extern "C" int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const 
                                   const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
                                   int32_t ninstr, int32_t op, const void* init) {
     return mapreduce_impl(st, R, shape, ndim, leaves, nleaves, program, ninstr, op, init, nullptr);
+}
+
+extern "C" int32_t b200_mapreduce_prepare(const b200_tensor* R, const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
+                                          int32_t nleaves, const uint8_t* program, int32_t ninstr, int32_t op) {
+    return mapreduce_impl(nullptr, R, shape, ndim, leaves, nleaves, program, ninstr, op, nullptr, nullptr, true);
 }
 
 extern "C" int32_t b200_mapreduce_allreduce(b200_peer_t peer, b200_stream_t st, const b200_tensor* R, const int64_t* shape,

@@ -82,6 +82,7 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
 // (1), report that there is none so that the caller interprets (0), or that it cannot be built
 // inside a stream capture (-1); compile it without launching.
 int jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n);
+int32_t jit_prepare_reduce(const Compiled& C, int out_dtype, int redop, int acc_dtype, int full);
 int32_t jit_prepare(const Compiled& C, int out_dtype);
 int jit_reduce_kernel(b200_stream_t st, const Compiled& C, int out_dtype, int redop, int acc_dtype, int full,
                       const void** kernel, int64_t* resident);

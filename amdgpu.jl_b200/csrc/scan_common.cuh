@@ -36,9 +36,7 @@ template <> struct ScanAcc<__half> { using type = float; };
 template <> struct ScanAcc<__nv_bfloat16> { using type = float; };
 template <typename T> __device__ __forceinline__ typename ScanAcc<T>::type scan_up(T v) { return v; }
 template <> __device__ __forceinline__ float scan_up<__half>(__half v) { return __half2float(v); }
-template <> __device__ __forceinline__ float scan_up<__nv_bfloat16>(__nv_bfloat16 v) {
-    return __uint_as_float((uint32_t)__bfloat16_as_ushort(v) << 16);      // exact: the upper half of a binary32
-}
+template <> __device__ __forceinline__ float scan_up<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T scan_down(typename ScanAcc<T>::type v) { return (T)v; }
 template <> __device__ __forceinline__ __half scan_down<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 scan_down<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }

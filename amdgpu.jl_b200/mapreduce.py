@@ -88,6 +88,17 @@ def prepared(f, op, R: ROCArray, A, init=None, stream: Stream | None = None):
     return launch
 
 
+def precompile(f, op, R: ROCArray, A) -> bool:
+    """Compiles the kernel ``mapreducedim!(f, op, R, A)`` would need, without launching anything
+    (no device needed).  False when the run-time compiler is unavailable."""
+    expr = _apply_f(f, A)
+    shape = expr.shape()
+    code, leaves, nleaves, _keep = expr.flatten()
+    shp = (C.c_int64 * max(1, len(shape)))(*shape)
+    t = R.tensor()
+    return lib.b200_mapreduce_prepare(C.byref(t), shp, len(shape), leaves, nleaves, code, len(code) // 2, _op_code(op)) == 0
+
+
 def _result_dtype(expr_dtype: int, opc: int) -> np.dtype:
     # Base.add_sum / mul_prod widen small integers; everything else keeps the mapped type.
     if opc in (_lib.RED_ADD, _lib.RED_MUL):

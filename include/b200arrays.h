@@ -222,6 +222,12 @@ int32_t b200_jit_stats(uint64_t out[4]);
 int32_t b200_mapreduce(b200_stream_t st, const b200_tensor* R, const int64_t* shape, int32_t ndim,
                        const b200_leaf* leaves, int32_t nleaves, const uint8_t* program,
                        int32_t ninstr, int32_t op, const void* init);
+/* Validates the same arguments and compiles the kernel that call would need, without launching
+ * (no stream, no device): the counterpart of b200_broadcast_prepare for reductions whose map is an
+ * expression.  B200_OK also when a kernel that is part of the library serves the call;
+ * B200_UNSUPPORTED when the run-time compiler is unavailable (the call itself then interprets). */
+int32_t b200_mapreduce_prepare(const b200_tensor* R, const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
+                               int32_t nleaves, const uint8_t* program, int32_t ninstr, int32_t op);
 
 /* replaces Base.accumulate!(op, B, A; init, dims) → AK.accumulate! (src/kernels/accumulate.jl:1-8).
  * B and A have equal shape and dtype; dim is 0-based; init is one HOST value of that dtype or

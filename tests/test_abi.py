@@ -64,3 +64,24 @@ def test_runtime_compiler_builds_a_kernel_without_a_device(pkg):
     assert after["compiled"] == before["compiled"] + 1
     assert B.precompile(o, B.exp(x.dot) * 3.0 - B.abs_(x.dot))               # other scalar: same kernel
     assert B.jit_stats()["compiled"] == after["compiled"]
+
+
+def test_runtime_compiler_builds_a_reduction_kernel_without_a_device(pkg):
+    """The same for mapreduce over an expression: b200_mapreduce_prepare compiles the specialised
+    reduction kernel (full reduction and reduction along one dimension)."""
+    class FakeBuffer:
+        ptr, freed, stream = 1 << 20, False, None
+
+    x = pkg.ROCArray(np.float32, (64, 64), _buf=FakeBuffer())
+    y = pkg.ROCArray(np.float32, (64, 64), _buf=FakeBuffer())
+    B = pkg.broadcast
+    if not B.precompile(pkg.ROCArray(np.float32, (64, 64), _buf=FakeBuffer()), x.dot - y.dot):
+        pytest.skip("libnvrtc is not installed here")
+    before = B.jit_stats()
+    assert pkg.mapreduce_precompile(None, "+", pkg.ROCArray(np.float32, 1, _buf=FakeBuffer()), x.dot * y.dot)
+    assert pkg.mapreduce_precompile(None, "max", pkg.ROCArray(np.float32, (1, 64), _buf=FakeBuffer()), B.abs_(x.dot - y.dot))
+    after = B.jit_stats()
+    assert after["compiled"] == before["compiled"] + 2 and after["failures"] == before["failures"]
+    # a plain sum of one dense array needs no compilation
+    assert pkg.mapreduce_precompile("identity", "+", pkg.ROCArray(np.float32, 1, _buf=FakeBuffer()), x)
+    assert B.jit_stats()["compiled"] == after["compiled"]
