@@ -22,8 +22,10 @@ def _positions(bools: ROCArray, stream: Stream):
     if bools.dtype != np.bool_:
         raise TypeError("the mask must be a Bool array")
     flat = bools.reshape(bools.size)
-    as_int = ROCArray(np.int64, flat.dims, stream=stream)
-    code = bytes((0, 0, 1, 7))                      # LEAF 0, CONVERT -> Int64
+    # positions fit Int32 below 2^31 entries: half the traffic of the scan and of the compaction
+    wide = flat.size >= (1 << 31) - 1
+    as_int = ROCArray(np.int64 if wide else np.int32, flat.dims, stream=stream)
+    code = bytes((0, 0, 1, 7 if wide else 6))       # LEAF 0, CONVERT -> Int64 / Int32
     leaves = Broadcasted.leaf(flat).flatten()[1]
     t = as_int.tensor()
     with_managed(stream, as_int, flat)

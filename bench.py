@@ -315,6 +315,25 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
             out["c4_sort_2p28_u32"] = {"ms": round(ms, 3), "Gkeys/s": round(n / ms / 1e6, 2), "model_GB/s": round(36 * n / ms / 1e6, 1),
                                        "frac_of_8TBs_model36B": round(36 * n / ms / 1e6 / NOMINAL_HBM_GBS, 3)}
         del v, o
+    # the consumers of the scan and of the sort (the "next" rows around the path): findall, logical
+    # indexing, reverse, x[ix]; algorithmic bytes = inputs read once + outputs written once
+    if want("next"):
+        n = (1 << 26) >> shrink
+        rng = np.random.default_rng(6)
+        mask_h = rng.random(n) < 0.5
+        nnz = int(mask_h.sum())
+        mask = pkg.ROCArray.from_host(mask_h)
+        xs = R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM01, seed=6)
+        def timed_alloc(fn, k):
+            def go():
+                fn().unsafe_free_()
+            return time_loop(pkg, st, go, reps(k))
+        rec("next_findall_2p26_bool", n + 8 * nnz, timed_alloc(lambda: pkg.findall(mask), 10))
+        rec("next_getindex_mask_2p26_f32", 5 * n + 4 * nnz, timed_alloc(lambda: pkg.getindex_mask(xs, mask), 10))
+        rec("next_reverse_2p26_f32", 8 * n, timed_alloc(lambda: pkg.reverse(xs), 10))
+        perm = pkg.sortperm(R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM01, seed=7))
+        rec("next_getindex_perm_2p26_f32", 16 * n, timed_alloc(lambda: pkg.getindex(xs, perm), 10))
+        del mask, xs, perm
     # yardsticks only: the vendor library kernels torch ships (CUB scan / radix sort, its own
     # reductions) on the same sizes, timed the same way on torch's stream.  Not part of any path
     # of this library; they say what "good" is on this box.

@@ -261,7 +261,7 @@ int32_t b200_sort(b200_stream_t st, const b200_tensor* x, int32_t rev);
 int32_t b200_sortperm(b200_stream_t st, const b200_tensor* ix, const b200_tensor* x, int32_t rev);
 
 /* replaces the scatter kernel of findall / logical indexing (src/kernels/indexing.jl:8-36).
- * `indices` = cumsum of the Bool mask as Int64 (b200_accumulate).  values == NULL: ys (Int64)
+ * `indices` = cumsum of the Bool mask as Int64 or Int32 (b200_accumulate).  values == NULL: ys (Int64)
  * receives the 1-based linear indices of the true entries; otherwise ys receives values[mask]. */
 int32_t b200_compact(b200_stream_t st, const b200_tensor* ys, const b200_tensor* bools,
                      const b200_tensor* indices, const b200_tensor* values);

@@ -80,3 +80,50 @@ def test_mask_along_one_dimension(gpu):
     assert none.dims == (3, 0)
     with pytest.raises(IndexError):
         gpu.getindex_mask_dim(gpu.ROCArray(np.float32, (3, 4)), gpu.ROCArray.from_host(np.zeros(3, bool)), 2)
+
+
+def test_vector_paths_and_their_edges(gpu):
+    """The 16-byte forms of reverse, gather and compaction and the shapes that fall back to the
+    element-wise forms: first dimensions that hold a whole number of vectors or not, every
+    element size, flips of several dimensions at once, operands that start off a 16-byte boundary
+    (views), lengths that are not a multiple of four, Int32 index vectors."""
+    rng = np.random.default_rng(3)
+    for dt in (np.uint8, np.float16, np.float32, np.float64):
+        for shape in ((64, 9, 5), (48,), (16, 3), (20, 6), (4096, 33)):
+            a = (rng.random(shape) * 200).astype(dt)
+            ad = gpu.ROCArray.from_host(a)
+            nd = len(shape)
+            for dims in [None] + list(range(1, nd + 1)) + ([(1, nd)] if nd > 1 else []):
+                sl = tuple(slice(None, None, -1) if (dims is None or d + 1 == dims or (isinstance(dims, tuple) and d + 1 in dims))
+                           else slice(None) for d in range(nd))
+                assert np.array_equal(gpu.reverse(ad, dims=dims).to_host(), a[sl]), (dt, shape, dims)
+    v = rng.integers(-1000, 1000, 10_003).astype(np.int32)
+    vd = gpu.ROCArray.from_host(v)
+    off = vd.view(1, 10_001)                                   # starts 4 bytes past a 16-byte boundary
+    assert np.array_equal(gpu.reverse(off).to_host(), v[1:10_001][::-1])
+    # gather: lengths around multiples of four, both index types, an index vector off the boundary
+    x = rng.standard_normal(5000).astype(np.float32)
+    xd = gpu.ROCArray.from_host(x)
+    for n in (1, 3, 4, 5, 1023, 1024, 4099):
+        for it in (np.int64, np.int32):
+            ix = rng.integers(1, 5001, n).astype(it)
+            assert np.array_equal(gpu.getindex(xd, gpu.ROCArray.from_host(ix)).to_host(), x[ix - 1]), (n, it)
+    ix = rng.integers(1, 5001, 2002).astype(np.int64)
+    ixd = gpu.ROCArray.from_host(ix)
+    assert np.array_equal(gpu.getindex(xd, ixd.view(1, 2002)).to_host(), x[ix[1:2002] - 1])
+    for dt in (np.uint8, np.float16, np.float64):
+        y = (rng.random(777) * 100).astype(dt)
+        ix = rng.integers(1, 778, 1001).astype(np.int64)
+        assert np.array_equal(gpu.getindex(gpu.ROCArray.from_host(y), gpu.ROCArray.from_host(ix)).to_host(), y[ix - 1])
+    # compaction: a mask that starts off the boundary, all element sizes, sparse and dense masks
+    for n in (5, 4096, 100_003):
+        for p in (0.01, 0.5, 0.99):
+            m = rng.random(n) < p
+            md = gpu.ROCArray.from_host(m)
+            want = np.flatnonzero(m) + 1
+            assert np.array_equal(gpu.findall(md).to_host(), want), (n, p)
+            if n > 8:
+                assert np.array_equal(gpu.findall(md.view(3, n)).to_host(), np.flatnonzero(m[3:]) + 1), (n, p)
+            for dt in (np.uint8, np.int16, np.float32, np.float64):
+                xs = (rng.random(n) * 100).astype(dt)
+                assert np.array_equal(gpu.getindex_mask(gpu.ROCArray.from_host(xs), md).to_host(), xs[m]), (n, p, dt)
