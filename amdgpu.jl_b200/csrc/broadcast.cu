@@ -536,6 +536,99 @@ static bool try_fixed(b200_stream_t st, const Compiled& C, const std::vector<Nod
     return false;
 }
 
+// ---- transposed operands --------------------------------------------------------------------------------
+// dst: m x n dense column-major (element (i, j) at i + j*m); src holds the same element at
+// i*ld + j, i.e. it is contiguous along j: a transposed matrix (or a view of one with leading
+// dimension ld).  Tiles through shared memory: the reads run along j, the writes along i, both in
+// whole lines; one tile per block.
+template <typename E, int TILE>
+__global__ void __launch_bounds__(256) transpose_copy_kernel(E* dst, const E* src, int64_t m, int64_t n, int64_t ld) {
+    __shared__ E tile[TILE][TILE + 1];
+    constexpr int ROWS = 256 / TILE;
+    const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
+    const int64_t tiles_i = (m + TILE - 1) / TILE, tiles_j = (n + TILE - 1) / TILE;
+    grid_dependency_wait();
+    for (int64_t t = blockIdx.x; t < tiles_i * tiles_j; t += gridDim.x) {
+        const int64_t i0 = (t % tiles_i) * TILE, j0 = (t / tiles_i) * TILE;
+#pragma unroll
+        for (int r = ty; r < TILE; r += ROWS) {
+            const int64_t i = i0 + r, j = j0 + tx;
+            if (i < m && j < n) tile[r][tx] = src[i * ld + j];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = ty; r < TILE; r += ROWS) {
+            const int64_t i = i0 + tx, j = j0 + r;
+            if (i < m && j < n) dst[i + j * m] = tile[tx][r];
+        }
+        __syncthreads();
+    }
+}
+
+static void launch_transpose_copy(b200_stream_t st, void* dst, const void* src, int bytes, int64_t m, int64_t n, int64_t ld) {
+    auto grid_for = [&](int tile) {
+        const int64_t tiles = ((m + tile - 1) / tile) * ((n + tile - 1) / tile);
+        return (unsigned)(tiles > 0x7fffffff ? 0x7fffffff : tiles);
+    };
+    switch (bytes) {
+        case 1: launch_overlapped(transpose_copy_kernel<uint8_t, 64>, grid_for(64), 256, 0, st->s, (uint8_t*)dst, (const uint8_t*)src, m, n, ld); break;
+        case 2: launch_overlapped(transpose_copy_kernel<uint16_t, 64>, grid_for(64), 256, 0, st->s, (uint16_t*)dst, (const uint16_t*)src, m, n, ld); break;
+        case 4: launch_overlapped(transpose_copy_kernel<uint32_t, 64>, grid_for(64), 256, 0, st->s, (uint32_t*)dst, (const uint32_t*)src, m, n, ld); break;
+        default: launch_overlapped(transpose_copy_kernel<uint64_t, 32>, grid_for(32), 256, 0, st->s, (uint64_t*)dst, (const uint64_t*)src, m, n, ld); break;
+    }
+}
+
+// Is `t`, seen in the index space `shape`, a transposed matrix: exactly two dimensions d0 < d1
+// longer than one, all of the leaf present (no broadcast along them), unit stride along d1 and a
+// leading dimension along d0?  Large enough for the detour through a dense copy to pay.
+static bool transposed_matrix(const b200_tensor& t, const int64_t* shape, int32_t ndim, int* d0, int* d1) {
+    int a = -1, b = -1, count = 0;
+    for (int d = 0; d < ndim; ++d) {
+        if (shape[d] <= 1) continue;
+        if (count == 0) a = d; else b = d;
+        ++count;
+    }
+    if (count != 2 || t.ndim <= b) return false;
+    if (t.shape[a] != shape[a] || t.shape[b] != shape[b]) return false;
+    if (t.stride[b] != 1 || t.stride[a] < shape[b]) return false;
+    if (shape[a] * shape[b] < (1 << 14)) return false;
+    *d0 = a; *d1 = b;
+    return true;
+}
+
+// Operands that are transposed matrices would be read across their lines (32 bytes fetched per
+// element used): they are first copied into dense form through shared-memory tiles, into the
+// stream's scratch, and the expression then runs on dense operands at streaming speed.  `fixed`
+// receives the leaves to use.  Without room for the copies the leaves stay as they are.
+int32_t densify_transposed_leaves(b200_stream_t st, const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
+                                  int32_t nleaves, b200_leaf* fixed) {
+    size_t total = 0;
+    int d0[B200_MAX_LEAVES], d1[B200_MAX_LEAVES];
+    bool take[B200_MAX_LEAVES];
+    for (int k = 0; k < nleaves; ++k) {
+        fixed[k] = leaves[k];
+        take[k] = !leaves[k].is_scalar && leaves[k].t.ptr && dtype_size(leaves[k].t.dtype) > 0 &&
+                  transposed_matrix(leaves[k].t, shape, ndim, &d0[k], &d1[k]);
+        if (take[k]) total += ((size_t)(shape[d0[k]] * shape[d1[k]]) * dtype_size(leaves[k].t.dtype) + 255) / 256 * 256;
+    }
+    if (total == 0) return B200_OK;
+    void* scr = nullptr;
+    if (scratch(st, total, &scr) != B200_OK) return B200_OK;        // no room: the strided path still works
+    unsigned char* p = reinterpret_cast<unsigned char*>(scr);
+    for (int k = 0; k < nleaves; ++k) {
+        if (!take[k]) continue;
+        const b200_tensor& t = leaves[k].t;
+        const int64_t m = shape[d0[k]], n = shape[d1[k]];
+        const int bytes = (int)dtype_size(t.dtype);
+        launch_transpose_copy(st, p, t.ptr, bytes, m, n, t.stride[d0[k]]);
+        fixed[k].t.ptr = p;
+        int64_t expect = 1;
+        for (int d = 0; d < t.ndim; ++d) { fixed[k].t.stride[d] = expect; expect *= t.shape[d]; }
+        p += ((size_t)(m * n) * bytes + 255) / 256 * 256;
+    }
+    return B200_OK;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -562,11 +655,31 @@ extern "C" int32_t b200_broadcast_prepare(const b200_tensor* out, const b200_lea
 extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, const b200_leaf* leaves,
                                   int32_t nleaves, const uint8_t* program, int32_t ninstr) {
     B200_TRY(enter(st));
+    StreamGuard guard(st);
     B200_TRY(check_tensor(out, "broadcast destination"));
     const int64_t n = tensor_numel(out);
     Compiled C;
     B200_TRY(compile_program(out->shape, out->ndim, leaves, nleaves, program, ninstr, out->dtype, &C));
     if (n == 0) return B200_OK;
+    if (!C.P.linear && leaves && nleaves > 0 && nleaves <= B200_MAX_LEAVES) {
+        // a plain copy of a transposed matrix goes straight into a dense destination
+        int d0 = 0, d1 = 0;
+        if (ninstr == 1 && program[0] == B200_OP_LEAF && !leaves[program[1]].is_scalar && leaves[program[1]].t.dtype == out->dtype &&
+            tensor_is_contiguous(out) && transposed_matrix(leaves[program[1]].t, out->shape, out->ndim, &d0, &d1)) {
+            const b200_tensor& src = leaves[program[1]].t;
+            const size_t bytes = dtype_size(src.dtype);
+            const uintptr_t s0 = reinterpret_cast<uintptr_t>(src.ptr);
+            const uintptr_t s1 = s0 + (size_t)((out->shape[d0] - 1) * src.stride[d0] + out->shape[d1]) * bytes;
+            const uintptr_t o0 = reinterpret_cast<uintptr_t>(out->ptr), o1 = o0 + (size_t)n * bytes;
+            if (s1 <= o0 || o1 <= s0) {           // source and destination apart (A .= A' goes through the copy below)
+                launch_transpose_copy(st, out->ptr, src.ptr, (int)bytes, out->shape[d0], out->shape[d1], src.stride[d0]);
+                return finish(st, "b200_broadcast");
+            }
+        }
+        b200_leaf fixed[B200_MAX_LEAVES];
+        B200_TRY(densify_transposed_leaves(st, out->shape, out->ndim, leaves, nleaves, fixed));
+        B200_TRY(compile_program(out->shape, out->ndim, fixed, nleaves, program, ninstr, out->dtype, &C));
+    }
     for (int d = 0; d < out->ndim; ++d)
         if (out->shape[d] > 1 && out->stride[d] == 0) return fail(B200_INVALID_ARG, "broadcast destination has a zero stride");
 

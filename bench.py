@@ -334,6 +334,14 @@ def run_suite(pkg, peak: float, only: str | None = None, shrink: int = 0, reps_s
         perm = pkg.sortperm(R.fill_random_(pkg.ROCArray(np.float32, n), R.UNIFORM01, seed=7))
         rec("next_getindex_perm_2p26_f32", 16 * n, timed_alloc(lambda: pkg.getindex(xs, perm), 10))
         del mask, xs, perm
+        # wrapped operands: a transposed matrix as source of a copy and as operand of a fused expression
+        m = 8192 >> (shrink // 2)
+        A = R.fill_random_(pkg.ROCArray(np.float32, (m, m)), R.UNIFORM01, seed=8)
+        Bm = R.fill_random_(pkg.ROCArray(np.float32, (m, m)), R.UNIFORM01, seed=9)
+        Cm = pkg.ROCArray(np.float32, (m, m))
+        rec("next_copy_transpose_8192_f32", 8 * m * m, time_loop(pkg, st, lambda: pkg.copyto_(Cm, A.transpose()), reps(5)))
+        rec("next_add_transpose_8192_f32", 12 * m * m, time_loop(pkg, st, pkg.broadcast.prepared(Cm, A.dot + Bm.transpose().dot), reps(5)))
+        del A, Bm, Cm
     # yardsticks only: the vendor library kernels torch ships (CUB scan / radix sort, its own
     # reductions) on the same sizes, timed the same way on torch's stream.  Not part of any path
     # of this library; they say what "good" is on this box.

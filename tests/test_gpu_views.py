@@ -136,3 +136,43 @@ def test_integer_vector_indexing(gpu):
     gpu.synchronize()
     assert gpu.sum(small) == 10.0
     del out
+
+
+def test_large_transposed_operands_go_through_tiles(gpu):
+    """Transposed matrices above 2^14 elements are copied into dense form through shared-memory
+    tiles before the expression runs (or straight into a dense destination for a plain copy):
+    every element size, extents that are not multiples of the tile, the transpose of a view with
+    a leading dimension, several transposed operands at once, a destination that aliases the
+    source, and a dimension of extent one between the two."""
+    rng = np.random.default_rng(13)
+    for dt in (np.uint8, np.float16, np.float32, np.int64):
+        for shape in ((200, 300), (129, 257), (1024, 64), (64, 1024), (131, 128)):
+            K = np.asfortranarray((rng.random(shape[::-1]) * 100).astype(dt))        # K.T has `shape`
+            Kd = gpu.ROCArray.from_host(K)
+            assert bits_equal(Kd.transpose().copy().to_host(), np.asfortranarray(K.T)), (dt, shape)
+            assert bits_equal(Kd.permutedims((2, 1)).to_host(), np.asfortranarray(K.T)), (dt, shape)
+    H, K, L = fa(rng, (300, 200)), fa(rng, (200, 300)), fa(rng, (200, 300))
+    A, B, Cc = gpu.ROCArray.from_host(H), gpu.ROCArray.from_host(K), gpu.ROCArray.from_host(L)
+    out = (A.dot + B.transpose().dot).materialize().to_host()
+    assert bits_equal(out, H + K.T)
+    out = (B.transpose().dot * Cc.transpose().dot + np.float32(0.5)).materialize().to_host()
+    assert bits_equal(out, (K.T * L.T + np.float32(0.5)).astype(np.float32))
+    # the transpose of a window of a larger matrix
+    Big = fa(rng, (400, 500))
+    Bd = gpu.ROCArray.from_host(Big)
+    win = Bd.subview(slice(10, 210), slice(5, 305))                               # 200 x 300, leading dimension 400
+    assert bits_equal(win.transpose().copy().to_host(), np.asfortranarray(Big[10:210, 5:305].T))
+    assert bits_equal((A.dot - win.transpose().dot).materialize().to_host(), H - Big[10:210, 5:305].T)
+    # A .= A' on a square matrix: the source is copied before the destination is written
+    S = fa(rng, (256, 256))
+    Sd = gpu.ROCArray.from_host(S)
+    gpu.materialize_(Sd, Sd.transpose().dot)
+    assert bits_equal(Sd.to_host(), np.asfortranarray(S.T))
+    # 3-d operand whose middle dimension has extent one
+    T = fa(rng, (150, 1, 180))
+    Td = gpu.ROCArray.from_host(T)
+    assert bits_equal(Td.permuteddims((3, 2, 1)).copy().to_host(), np.asfortranarray(T.transpose(2, 1, 0)))
+    # mixed element types still take the evaluator after the copy
+    I = np.asfortranarray(rng.integers(-50, 50, (200, 300)).astype(np.int32))
+    out = (gpu.ROCArray.from_host(I).transpose().dot * A.dot).materialize().to_host()
+    assert bits_equal(out, (I.T.astype(np.float32) * H).astype(np.float32))
