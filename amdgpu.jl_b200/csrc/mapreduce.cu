@@ -65,6 +65,47 @@ __device__ __forceinline__ Acc map_elem(Tin x) {
     return (Acc)v;
 }
 
+// Extrema of 16-bit floats are exact in the element type: pairs are folded with ONE packed
+// instruction per 32-bit word and widened once after the loop, instead of a conversion and a
+// binary32 max per element.  Same semantics as the binary32 forms (NaN-propagating, -0.0 below
+// +0.0).  Used for f = identity or abs.
+template <typename Tin, int MAP, int OP>
+constexpr bool kPackedExtremum = (std::is_same<Tin, __half>::value || std::is_same<Tin, __nv_bfloat16>::value) &&
+                                 (OP == B200_RED_MAX || OP == B200_RED_MIN) && (MAP == MAP_ID || MAP == MAP_ABS);
+template <typename Tin, int OP>
+__device__ __forceinline__ uint32_t packed_extremum(uint32_t a, uint32_t b) {
+    uint32_t r;
+    if constexpr (std::is_same<Tin, __half>::value) {
+        if constexpr (OP == B200_RED_MAX) asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        else asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    } else {
+        if constexpr (OP == B200_RED_MAX) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        else asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    }
+    return r;
+}
+// -Inf (max) or +Inf (min) in both halves.
+template <typename Tin, int OP>
+__device__ __forceinline__ uint32_t packed_identity() {
+    const uint32_t inf = std::is_same<Tin, __half>::value ? 0x7c00u : 0x7f80u;
+    const uint32_t one = OP == B200_RED_MAX ? (inf | 0x8000u) : inf;
+    return one | (one << 16);
+}
+template <typename Tin, int MAP, int OP>
+__device__ __forceinline__ void packed_fold(uint32_t pacc[4], uint4 w) {
+    if constexpr (MAP == MAP_ABS) { w.x &= 0x7fff7fffu; w.y &= 0x7fff7fffu; w.z &= 0x7fff7fffu; w.w &= 0x7fff7fffu; }
+    pacc[0] = packed_extremum<Tin, OP>(pacc[0], w.x);
+    pacc[1] = packed_extremum<Tin, OP>(pacc[1], w.y);
+    pacc[2] = packed_extremum<Tin, OP>(pacc[2], w.z);
+    pacc[3] = packed_extremum<Tin, OP>(pacc[3], w.w);
+}
+template <typename Tin>
+__device__ __forceinline__ float unpack16(uint32_t w, int hi) {
+    const unsigned short bits = (unsigned short)(hi ? (w >> 16) : (w & 0xffffu));
+    if constexpr (std::is_same<Tin, __half>::value) return __half2float(__ushort_as_half(bits));
+    else return __bfloat162float(__ushort_as_bfloat16(bits));
+}
+
 template <typename Acc>
 __device__ __forceinline__ void store_result(void* R, int dt, int64_t idx, Acc v) {
     store_bits(R, dtype_bytes(dt), idx, encode<uint64_t>(dt, raw_of<uint64_t>(v)));
@@ -106,19 +147,35 @@ __device__ __forceinline__ void segment_accumulate(const Tin* p, int64_t n, int 
     const int64_t nv = (n - head) / V;
     constexpr int U = 4;
     int64_t i = tid;
-    for (; i + (int64_t)(U - 1) * nthr < nv; i += (int64_t)U * nthr) {
-        VT v[U];
+    if constexpr (kPackedExtremum<Tin, MAP, OP> && V == 8) {
+        uint32_t pacc[4];
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = __builtin_bit_cast(VT, __ldcs(vp + i + (int64_t)u * nthr));
+        for (int q = 0; q < 4; ++q) pacc[q] = packed_identity<Tin, OP>();
+        for (; i + (int64_t)(U - 1) * nthr < nv; i += (int64_t)U * nthr) {
+            uint4 w[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u)
+            for (int u = 0; u < U; ++u) w[u] = __ldcs(vp + i + (int64_t)u * nthr);
 #pragma unroll
-            for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v[u].v[k]));
-    }
-    for (; i < nv; i += nthr) {
-        VT v = __builtin_bit_cast(VT, __ldcs(vp + i));
+            for (int u = 0; u < U; ++u) packed_fold<Tin, MAP, OP>(pacc, w[u]);
+        }
+        for (; i < nv; i += nthr) packed_fold<Tin, MAP, OP>(pacc, __ldcs(vp + i));
 #pragma unroll
-        for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v.v[k]));
+        for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], (Acc)unpack16<Tin>(pacc[k / 2], k & 1));
+    } else {
+        for (; i + (int64_t)(U - 1) * nthr < nv; i += (int64_t)U * nthr) {
+            VT v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) v[u] = __builtin_bit_cast(VT, __ldcs(vp + i + (int64_t)u * nthr));
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v[u].v[k]));
+        }
+        for (; i < nv; i += nthr) {
+            VT v = __builtin_bit_cast(VT, __ldcs(vp + i));
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], map_elem<Tin, Acc, MAP>(v.v[k]));
+        }
     }
     const int64_t done = head + nv * V;
     if (tid < n - done) acc[0] = red_apply<Acc, OP>(acc[0], map_elem<Tin, Acc, MAP>(p[done + tid]));
@@ -349,6 +406,21 @@ __device__ __forceinline__ void strided_body(const Tin* A, const StridedPlan& pl
             const Tin* base = A + k0 + pl.K * (pl.L * m);
             constexpr int U = 8;
             int64_t l = lbeg + ty;
+            if constexpr (kPackedExtremum<Tin, MAP, OP> && V == 8) {
+                uint32_t pacc[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) pacc[q] = packed_identity<Tin, OP>();
+                for (; l + (int64_t)(U - 1) * pl.ly < lend; l += (int64_t)U * pl.ly) {
+                    uint4 w[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) w[u] = __ldcs(reinterpret_cast<const uint4*>(base + pl.K * (l + (int64_t)u * pl.ly)));
+#pragma unroll
+                    for (int u = 0; u < U; ++u) packed_fold<Tin, MAP, OP>(pacc, w[u]);
+                }
+                for (; l < lend; l += pl.ly) packed_fold<Tin, MAP, OP>(pacc, __ldcs(reinterpret_cast<const uint4*>(base + pl.K * l)));
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] = red_apply<Acc, OP>(acc[k], (Acc)unpack16<Tin>(pacc[k / 2], k & 1));
+            }
             for (; l + (int64_t)(U - 1) * pl.ly < lend; l += (int64_t)U * pl.ly) {
                 VT v[U];
 #pragma unroll

@@ -168,3 +168,55 @@ def test_run_to_run_determinism(gpu):
     assert len(set(a)) == 1
     b = [gpu.sum(A, dims=2).to_host().tobytes() for _ in range(3)]
     assert len(set(b)) == 1
+
+
+@pytest.mark.parametrize("dt", [np.float16, "bf16"])
+def test_packed_extrema_of_16_bit_floats(gpu, dt):
+    """maximum / minimum (and their abs forms) of Float16 / BFloat16 fold pairs with one packed
+    instruction; the results must be the same bits a widened fold gives: NaN wins wherever one
+    occurs, -0.0 is below +0.0, infinities and subnormals pass through - along both dimensions of
+    a matrix whose first dimension takes the 16-byte path, and for long vectors."""
+    if dt == "bf16":
+        if BF16 is None:
+            pytest.skip("no bfloat16 host type")
+        dt = BF16
+    dt = np.dtype(dt)
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((512, 300)).astype(np.float32)
+    a[rng.random(a.shape) < 0.05] = 0.0
+    a[rng.random(a.shape) < 0.05] = -0.0
+    a[7, 11] = np.inf
+    a[100, 200] = -np.inf
+    a[5, :] = np.float32(6e-8)                                   # subnormal in Float16
+    a[:, 17] = np.where(np.arange(512) % 2 == 0, 0.0, -0.0)        # a column of zeros of both signs
+    a[33, :] = -0.0
+    a = a.astype(dt)
+    a[200, 3] = np.nan
+    a[3, 250] = np.nan
+    ad = gpu.ROCArray.from_host(a)
+    wide = a.astype(np.float32)
+
+    def fold(x, op, axis):
+        nan = np.isnan(x).any(axis=axis, keepdims=True)
+        r = (np.max if op == "max" else np.min)(np.where(np.isnan(x), 0, x), axis=axis, keepdims=True)
+        # zeros: max is +0.0 if any +0.0 took part, min is -0.0 if any -0.0 did
+        pz = ((x == 0) & ~np.signbit(x)).any(axis=axis, keepdims=True)
+        nz = ((x == 0) & np.signbit(x)).any(axis=axis, keepdims=True)
+        zero = r == 0
+        r = np.where(zero & (op == "max"), np.where(pz, 0.0, -0.0), r)
+        r = np.where(zero & (op == "min"), np.where(nz, -0.0, 0.0), r)
+        return np.where(nan, np.nan, r).astype(np.float32)
+
+    for f, src in ((None, wide), ("abs", np.abs(wide))):
+        for op, fn in (("max", gpu.maximum), ("min", gpu.minimum)):
+            for dims, axis in ((1, 0), (2, 1)):
+                got = (fn(ad, dims=dims) if f is None else gpu.mapreduce(f, op, ad, dims=dims)).to_host().astype(np.float32)
+                want = fold(src, op, axis)
+                assert np.array_equal(np.isnan(got), np.isnan(want)), (f, op, dims)
+                ok = ~np.isnan(want)
+                assert np.array_equal(got[ok], want[ok]) and np.array_equal(np.signbit(got[ok]), np.signbit(want[ok])), (f, op, dims)
+    v = rng.standard_normal(1_000_003).astype(dt)
+    vd = gpu.ROCArray.from_host(v)
+    assert dt.type(gpu.maximum(vd)) == v.astype(np.float32).max() and dt.type(gpu.minimum(vd)) == v.astype(np.float32).min()
+    v[777_777] = np.nan
+    assert np.isnan(gpu.maximum(gpu.ROCArray.from_host(v)))
