@@ -536,95 +536,138 @@ static bool try_fixed(b200_stream_t st, const Compiled& C, const std::vector<Nod
     return false;
 }
 
-// ---- transposed operands --------------------------------------------------------------------------------
-// dst: m x n dense column-major (element (i, j) at i + j*m); src holds the same element at
-// i*ld + j, i.e. it is contiguous along j: a transposed matrix (or a view of one with leading
-// dimension ld).  Tiles through shared memory: the reads run along j, the writes along i, both in
-// whole lines; one tile per block.
+// ---- permuted operands ------------------------------------------------------------------------------------
+// An operand whose unit-stride dimension is not the first long dimension of the index space (a
+// transposed matrix, a PermutedDimsArray) would be read across its lines - 32 bytes fetched per
+// element used.  Such operands are copied into dense form first, through shared-memory tiles over
+// the pair (a, b): a = first long dimension of the index space (unit stride in the copy),
+// b = the operand's own unit-stride dimension.  Reads run along b, writes along a, both in whole
+// lines; all other dimensions are batch.  One tile per block.
+struct PermutePlan {
+    int32_t ndim, a, b;
+    int64_t shape[B200_MAX_DIMS];
+    int64_t sstride[B200_MAX_DIMS];     // operand strides (elements); sstride[b] == 1
+    int64_t dstride[B200_MAX_DIMS];     // dense strides of the copy; dstride[a] == 1
+    int64_t tiles_a, tiles_b, nbatch;
+};
+
 template <typename E, int TILE>
-__global__ void __launch_bounds__(256) transpose_copy_kernel(E* dst, const E* src, int64_t m, int64_t n, int64_t ld) {
+__global__ void __launch_bounds__(256) permute_copy_kernel(E* dst, const E* src, const __grid_constant__ PermutePlan pl) {
     __shared__ E tile[TILE][TILE + 1];
     constexpr int ROWS = 256 / TILE;
     const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
-    const int64_t tiles_i = (m + TILE - 1) / TILE, tiles_j = (n + TILE - 1) / TILE;
+    const int64_t m = pl.shape[pl.a], n = pl.shape[pl.b];
+    const int64_t sa = pl.sstride[pl.a], db = pl.dstride[pl.b];
+    const int64_t per_batch = pl.tiles_a * pl.tiles_b;
     grid_dependency_wait();
-    for (int64_t t = blockIdx.x; t < tiles_i * tiles_j; t += gridDim.x) {
-        const int64_t i0 = (t % tiles_i) * TILE, j0 = (t / tiles_i) * TILE;
+    for (int64_t t = blockIdx.x; t < per_batch * pl.nbatch; t += gridDim.x) {
+        int64_t batch = t / per_batch;
+        const int64_t in_batch = t - batch * per_batch;
+        const int64_t i0 = (in_batch % pl.tiles_a) * TILE, j0 = (in_batch / pl.tiles_a) * TILE;
+        int64_t soff = 0, doff = 0;
+        for (int d = 0; d < pl.ndim; ++d) {
+            if (d == pl.a || d == pl.b) continue;
+            const int64_t e = pl.shape[d];
+            const int64_t q = batch / e;
+            const int64_t c = batch - q * e;
+            soff += c * pl.sstride[d];
+            doff += c * pl.dstride[d];
+            batch = q;
+        }
 #pragma unroll
         for (int r = ty; r < TILE; r += ROWS) {
             const int64_t i = i0 + r, j = j0 + tx;
-            if (i < m && j < n) tile[r][tx] = src[i * ld + j];
+            if (i < m && j < n) tile[r][tx] = src[soff + i * sa + j];
         }
         __syncthreads();
 #pragma unroll
         for (int r = ty; r < TILE; r += ROWS) {
             const int64_t i = i0 + tx, j = j0 + r;
-            if (i < m && j < n) dst[i + j * m] = tile[tx][r];
+            if (i < m && j < n) dst[doff + i + j * db] = tile[tx][r];
         }
         __syncthreads();
     }
 }
 
-static void launch_transpose_copy(b200_stream_t st, void* dst, const void* src, int bytes, int64_t m, int64_t n, int64_t ld) {
-    auto grid_for = [&](int tile) {
-        const int64_t tiles = ((m + tile - 1) / tile) * ((n + tile - 1) / tile);
-        return (unsigned)(tiles > 0x7fffffff ? 0x7fffffff : tiles);
-    };
-    switch (bytes) {
-        case 1: launch_overlapped(transpose_copy_kernel<uint8_t, 64>, grid_for(64), 256, 0, st->s, (uint8_t*)dst, (const uint8_t*)src, m, n, ld); break;
-        case 2: launch_overlapped(transpose_copy_kernel<uint16_t, 64>, grid_for(64), 256, 0, st->s, (uint16_t*)dst, (const uint16_t*)src, m, n, ld); break;
-        case 4: launch_overlapped(transpose_copy_kernel<uint32_t, 64>, grid_for(64), 256, 0, st->s, (uint32_t*)dst, (const uint32_t*)src, m, n, ld); break;
-        default: launch_overlapped(transpose_copy_kernel<uint64_t, 32>, grid_for(32), 256, 0, st->s, (uint64_t*)dst, (const uint64_t*)src, m, n, ld); break;
-    }
-}
-
-// Is `t`, seen in the index space `shape`, a transposed matrix: exactly two dimensions d0 < d1
-// longer than one, all of the leaf present (no broadcast along them), unit stride along d1 and a
-// leading dimension along d0?  Large enough for the detour through a dense copy to pay.
-static bool transposed_matrix(const b200_tensor& t, const int64_t* shape, int32_t ndim, int* d0, int* d1) {
-    int a = -1, b = -1, count = 0;
+// Does `t`, seen in the index space `shape`, call for the tiled copy?  It must cover the index
+// space (no broadcast along a long dimension), its unit-stride dimension b must differ from the
+// first long dimension a, and both must be long enough for tiles to pay.
+static bool permuted_operand(const b200_tensor& t, const int64_t* shape, int32_t ndim, PermutePlan* pl) {
+    int a = -1, b = -1;
+    int64_t numel = 1;
     for (int d = 0; d < ndim; ++d) {
         if (shape[d] <= 1) continue;
-        if (count == 0) a = d; else b = d;
-        ++count;
+        if (d >= t.ndim || t.shape[d] != shape[d] || t.stride[d] == 0) return false;
+        if (a < 0) a = d;
+        if (t.stride[d] == 1 && b < 0) b = d;
+        numel *= shape[d];
     }
-    if (count != 2 || t.ndim <= b) return false;
-    if (t.shape[a] != shape[a] || t.shape[b] != shape[b]) return false;
-    if (t.stride[b] != 1 || t.stride[a] < shape[b]) return false;
-    if (shape[a] * shape[b] < (1 << 14)) return false;
-    *d0 = a; *d1 = b;
+    if (a < 0 || b < 0 || a == b || t.stride[a] == 1) return false;
+    if (shape[a] < 8 || shape[b] < 8 || numel < (1 << 14)) return false;
+    *pl = PermutePlan{};
+    pl->ndim = ndim; pl->a = a; pl->b = b;
+    int64_t expect = 1;
+    pl->nbatch = 1;
+    for (int d = 0; d < ndim; ++d) {
+        pl->shape[d] = shape[d];
+        pl->sstride[d] = (d < t.ndim && shape[d] > 1) ? t.stride[d] : 0;
+        pl->dstride[d] = expect;
+        expect *= shape[d];
+        if (d != a && d != b) pl->nbatch *= shape[d];
+    }
     return true;
 }
 
-// Operands that are transposed matrices would be read across their lines (32 bytes fetched per
-// element used): they are first copied into dense form through shared-memory tiles, into the
-// stream's scratch, and the expression then runs on dense operands at streaming speed.  `fixed`
-// receives the leaves to use.  Without room for the copies the leaves stay as they are.
-int32_t densify_transposed_leaves(b200_stream_t st, const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
-                                  int32_t nleaves, b200_leaf* fixed) {
+static void launch_permute_copy(b200_stream_t st, void* dst, const void* src, int bytes, PermutePlan pl) {
+    const int tile = bytes == 8 ? 32 : 64;
+    pl.tiles_a = (pl.shape[pl.a] + tile - 1) / tile;
+    pl.tiles_b = (pl.shape[pl.b] + tile - 1) / tile;
+    const int64_t tiles = pl.tiles_a * pl.tiles_b * pl.nbatch;
+    const unsigned grid = (unsigned)(tiles > 0x7fffffff ? 0x7fffffff : tiles);
+    switch (bytes) {
+        case 1: launch_overlapped(permute_copy_kernel<uint8_t, 64>, grid, 256, 0, st->s, (uint8_t*)dst, (const uint8_t*)src, pl); break;
+        case 2: launch_overlapped(permute_copy_kernel<uint16_t, 64>, grid, 256, 0, st->s, (uint16_t*)dst, (const uint16_t*)src, pl); break;
+        case 4: launch_overlapped(permute_copy_kernel<uint32_t, 64>, grid, 256, 0, st->s, (uint32_t*)dst, (const uint32_t*)src, pl); break;
+        default: launch_overlapped(permute_copy_kernel<uint64_t, 32>, grid, 256, 0, st->s, (uint64_t*)dst, (const uint64_t*)src, pl); break;
+    }
+}
+
+// Byte range [lo, hi) an operand with these strides touches.
+static void operand_span(const b200_tensor& t, const PermutePlan& pl, uintptr_t* lo, uintptr_t* hi) {
+    int64_t last = 0;
+    for (int d = 0; d < pl.ndim; ++d) if (pl.shape[d] > 1) last += (pl.shape[d] - 1) * pl.sstride[d];
+    *lo = reinterpret_cast<uintptr_t>(t.ptr);
+    *hi = *lo + (size_t)(last + 1) * dtype_size(t.dtype);
+}
+
+// `fixed` receives the leaves to use: permuted operands replaced by dense copies in the stream's
+// scratch.  Without room for the copies the leaves stay as they are (the strided path works).
+int32_t densify_permuted_leaves(b200_stream_t st, const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
+                                int32_t nleaves, b200_leaf* fixed) {
     size_t total = 0;
-    int d0[B200_MAX_LEAVES], d1[B200_MAX_LEAVES];
+    PermutePlan plan[B200_MAX_LEAVES];
     bool take[B200_MAX_LEAVES];
+    int64_t numel = 1;
+    for (int d = 0; d < ndim; ++d) numel *= shape[d];
     for (int k = 0; k < nleaves; ++k) {
         fixed[k] = leaves[k];
         take[k] = !leaves[k].is_scalar && leaves[k].t.ptr && dtype_size(leaves[k].t.dtype) > 0 &&
-                  transposed_matrix(leaves[k].t, shape, ndim, &d0[k], &d1[k]);
-        if (take[k]) total += ((size_t)(shape[d0[k]] * shape[d1[k]]) * dtype_size(leaves[k].t.dtype) + 255) / 256 * 256;
+                  permuted_operand(leaves[k].t, shape, ndim, &plan[k]);
+        if (take[k]) total += ((size_t)numel * dtype_size(leaves[k].t.dtype) + 255) / 256 * 256;
     }
     if (total == 0) return B200_OK;
     void* scr = nullptr;
-    if (scratch(st, total, &scr) != B200_OK) return B200_OK;        // no room: the strided path still works
+    if (scratch(st, total, &scr) != B200_OK) return B200_OK;
     unsigned char* p = reinterpret_cast<unsigned char*>(scr);
     for (int k = 0; k < nleaves; ++k) {
         if (!take[k]) continue;
         const b200_tensor& t = leaves[k].t;
-        const int64_t m = shape[d0[k]], n = shape[d1[k]];
         const int bytes = (int)dtype_size(t.dtype);
-        launch_transpose_copy(st, p, t.ptr, bytes, m, n, t.stride[d0[k]]);
+        launch_permute_copy(st, p, t.ptr, bytes, plan[k]);
         fixed[k].t.ptr = p;
-        int64_t expect = 1;
-        for (int d = 0; d < t.ndim; ++d) { fixed[k].t.stride[d] = expect; expect *= t.shape[d]; }
-        p += ((size_t)(m * n) * bytes + 255) / 256 * 256;
+        fixed[k].t.ndim = ndim;
+        for (int d = 0; d < ndim; ++d) { fixed[k].t.shape[d] = shape[d]; fixed[k].t.stride[d] = plan[k].dstride[d]; }
+        p += ((size_t)numel * bytes + 255) / 256 * 256;
     }
     return B200_OK;
 }
@@ -662,22 +705,21 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
     B200_TRY(compile_program(out->shape, out->ndim, leaves, nleaves, program, ninstr, out->dtype, &C));
     if (n == 0) return B200_OK;
     if (!C.P.linear && leaves && nleaves > 0 && nleaves <= B200_MAX_LEAVES) {
-        // a plain copy of a transposed matrix goes straight into a dense destination
-        int d0 = 0, d1 = 0;
+        // a plain copy of a permuted operand goes straight into a dense destination
+        PermutePlan pp;
         if (ninstr == 1 && program[0] == B200_OP_LEAF && !leaves[program[1]].is_scalar && leaves[program[1]].t.dtype == out->dtype &&
-            tensor_is_contiguous(out) && transposed_matrix(leaves[program[1]].t, out->shape, out->ndim, &d0, &d1)) {
+            tensor_is_contiguous(out) && permuted_operand(leaves[program[1]].t, out->shape, out->ndim, &pp)) {
             const b200_tensor& src = leaves[program[1]].t;
-            const size_t bytes = dtype_size(src.dtype);
-            const uintptr_t s0 = reinterpret_cast<uintptr_t>(src.ptr);
-            const uintptr_t s1 = s0 + (size_t)((out->shape[d0] - 1) * src.stride[d0] + out->shape[d1]) * bytes;
-            const uintptr_t o0 = reinterpret_cast<uintptr_t>(out->ptr), o1 = o0 + (size_t)n * bytes;
+            uintptr_t s0, s1;
+            operand_span(src, pp, &s0, &s1);
+            const uintptr_t o0 = reinterpret_cast<uintptr_t>(out->ptr), o1 = o0 + (size_t)n * dtype_size(out->dtype);
             if (s1 <= o0 || o1 <= s0) {           // source and destination apart (A .= A' goes through the copy below)
-                launch_transpose_copy(st, out->ptr, src.ptr, (int)bytes, out->shape[d0], out->shape[d1], src.stride[d0]);
+                launch_permute_copy(st, out->ptr, src.ptr, (int)dtype_size(src.dtype), pp);
                 return finish(st, "b200_broadcast");
             }
         }
         b200_leaf fixed[B200_MAX_LEAVES];
-        B200_TRY(densify_transposed_leaves(st, out->shape, out->ndim, leaves, nleaves, fixed));
+        B200_TRY(densify_permuted_leaves(st, out->shape, out->ndim, leaves, nleaves, fixed));
         B200_TRY(compile_program(out->shape, out->ndim, fixed, nleaves, program, ninstr, out->dtype, &C));
     }
     for (int d = 0; d < out->ndim; ++d)

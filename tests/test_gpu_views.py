@@ -176,3 +176,29 @@ def test_large_transposed_operands_go_through_tiles(gpu):
     I = np.asfortranarray(rng.integers(-50, 50, (200, 300)).astype(np.int32))
     out = (gpu.ROCArray.from_host(I).transpose().dot * A.dot).materialize().to_host()
     assert bits_equal(out, (I.T.astype(np.float32) * H).astype(np.float32))
+
+
+def test_permuted_operands_of_higher_rank(gpu):
+    """PermutedDimsArray operands whose unit-stride dimension is not the first one take the tiled
+    copy with the remaining dimensions as batch: every permutation of a 3-d array, a 4-d case,
+    extents that are not multiples of the tile, 2- and 8-byte elements, and use inside a fused
+    expression next to a dense operand."""
+    import itertools
+    rng = np.random.default_rng(14)
+    H = fa(rng, (40, 50, 60))
+    A = gpu.ROCArray.from_host(H)
+    for perm in itertools.permutations((1, 2, 3)):
+        ref = np.asfortranarray(H.transpose(tuple(p - 1 for p in perm)))
+        assert bits_equal(A.permuteddims(perm).copy().to_host(), ref), perm
+        D = gpu.ROCArray.from_host(np.asfortranarray(ref * np.float32(0.5)))
+        out = (A.permuteddims(perm).dot + D.dot).materialize().to_host()
+        assert bits_equal(out, ref + ref * np.float32(0.5)), perm
+    for dt in (np.float16, np.int64):
+        K = np.asfortranarray((rng.random((33, 70, 9, 21)) * 100).astype(dt))
+        Kd = gpu.ROCArray.from_host(K)
+        for perm in ((2, 1, 3, 4), (4, 3, 2, 1), (3, 4, 1, 2), (2, 4, 1, 3)):
+            ref = np.asfortranarray(K.transpose(tuple(p - 1 for p in perm)))
+            assert bits_equal(Kd.permutedims(perm).to_host(), ref), (dt, perm)
+    # short first dimension: stays on the strided path and must still be right
+    S = fa(rng, (3000, 5))
+    assert bits_equal(gpu.ROCArray.from_host(S).transpose().copy().to_host(), np.asfortranarray(S.T))
