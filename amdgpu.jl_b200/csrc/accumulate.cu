@@ -799,6 +799,209 @@ static int32_t launch_scan_strided(b200_stream_t st, const void* A, void* B, con
     return B200_OK;
 }
 
+// ---- scan along a strided dimension with a few columns (2 <= K <= 4) -----------------------------------
+// cumsum(A; dims=2) of a 3 x 1 000 000 matrix and the like: a handful of interleaved columns, each
+// very long.  A tile is 256 * RPT consecutive ROWS, i.e. one contiguous piece of memory that holds
+// all K columns of those rows; a thread takes RPT rows (whole 16-byte vectors), scans its K columns
+// in registers, threads and warps are stitched with shuffles and shared memory, and tiles are
+// chained per column with the aggregate / inclusive-prefix protocol of the 1-D scan - warp k
+// looks back for column k over a 512-tile window.  Memory is read once and written once, in whole
+// lines, where the per-column kernels read every line K times with stride-K accesses.
+constexpr int kFcThreads = 256;
+constexpr int kFcWarps = kFcThreads / 32;
+constexpr int kFcWindow = 16;                        // descriptors per lane and look-back round: 512 tiles
+// sixteen rows per thread (eight for 8-byte elements): a million rows are 245 (489) tiles, which one
+// look-back round covers - under load every dependent descriptor read costs 2-3 us
+__host__ __device__ constexpr int fc_rows_per_thread(size_t elem) { return elem >= 8 ? 8 : 16; }      // (2- and 4-byte elements are dispatched)
+
+template <typename T, int OP, int KC>
+__global__ void __launch_bounds__(kFcThreads)
+scan_fewcols_kernel(const T* A, T* B, ScanPlan pl, void* flag_mem, unsigned int* ticket, int32_t* err_word) {
+    using Acc = typename ScanAcc<T>::type;
+    constexpr int RPT = fc_rows_per_thread(sizeof(T));   // rows per thread
+    constexpr int E = RPT * KC;                      // elements per thread, element e = row e / KC, column e % KC
+    constexpr int ROWS = kFcThreads * RPT;           // rows per tile
+    constexpr int VE = 16 / sizeof(T);               // elements per 16-byte vector
+    constexpr int NV = E / VE;                       // vectors per thread (RPT is a multiple of VE)
+    using VT = Vec<T, VE>;
+    static_assert(KC <= kFcWarps, "one warp per column does the look-back");
+    __shared__ long long s_tile;
+    __shared__ Acc s_wtot[kFcWarps][KC];
+    __shared__ Acc s_coltot[KC];
+    __shared__ Acc s_prefix[KC];
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        const unsigned int t = atomicAdd(ticket, 1u);
+        if ((int64_t)t == pl.ntiles - 1) *ticket = 0;   // nobody takes a ticket after the last tile
+        s_tile = t;
+        s_abort = 0;
+    }
+    __syncthreads();
+    const int64_t NT = pl.tiles_per_col;
+    const int64_t id = s_tile;
+    const int64_t tt = id / pl.M, m = id - tt * pl.M;     // all slabs' band tt before band tt + 1
+    TileState<Acc> state;
+    state.bind(flag_mem, pl.value_mem, pl.M * KC * NT, pl.epoch);
+    const int64_t slab = m * pl.K * pl.L;
+    const int64_t row0 = tt * ROWS + (int64_t)tid * RPT;
+    const bool full = tt * ROWS + ROWS <= pl.L;
+    const T* src = A + slab + row0 * KC;
+    T* dst = B + slab + row0 * KC;
+
+    Acc x[E];
+    if (full && pl.vec_ok) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const VT v = __builtin_bit_cast(VT, __ldcs(reinterpret_cast<const uint4*>(src) + j));
+#pragma unroll
+            for (int q = 0; q < VE; ++q) x[j * VE + q] = scan_up<T>(v.v[q]);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) x[e] = (row0 + e / KC < pl.L) ? scan_up<T>(src[e]) : scan_identity<Acc, OP>();
+    }
+    // down the thread's rows, per column
+#pragma unroll
+    for (int e = KC; e < E; ++e) x[e] = scan_apply<Acc, OP>(x[e - KC], x[e]);
+    // across the threads of the warp, then the warps
+    Acc wex[KC];                                      // exclusive prefix of this thread inside its warp
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+        const Acc inc = warp_scan_inclusive<Acc, OP>(x[(RPT - 1) * KC + k], lane);
+        Acc ex = __shfl_up_sync(0xffffffffu, inc, 1);
+        if (lane == 0) ex = scan_identity<Acc, OP>();
+        wex[k] = ex;
+        if (lane == 31) s_wtot[warp][k] = inc;
+    }
+    __syncthreads();
+    if (tid < KC) {
+        Acc total = s_wtot[0][tid];
+#pragma unroll
+        for (int w = 1; w < kFcWarps; ++w) total = scan_apply<Acc, OP>(total, s_wtot[w][tid]);
+        s_coltot[tid] = total;
+        const int64_t d = (m * KC + tid) * NT + tt;
+        if (tt == 0) {
+            const Acc seed = pl.has_init ? scan_seed<T>(pl) : scan_identity<Acc, OP>();
+            s_prefix[tid] = seed;
+            state.publish(d, FLAG_PREFIX, pl.has_init ? scan_apply<Acc, OP>(seed, total) : total);
+        } else {
+            state.publish(d, FLAG_AGGREGATE, total);
+        }
+    }
+    __syncthreads();
+    // look-back: warp k resolves column k
+    if (warp < KC && tt > 0) {
+        const int64_t base = (m * KC + warp) * NT;
+        int64_t look = tt - 1;
+        Acc running = scan_identity<Acc, OP>();
+        bool running_set = false, failed = false;
+        bool done = false;
+        while (!done && !failed) {
+            // A round covers 32 * kFcWindow tiles: slab j holds the tiles look - 32 j - lane, so the
+            // nearest 32 tiles - the ones most likely still EMPTY - sit in 32 different lanes and
+            // are polled side by side.  All reads of the round go out together.
+            uint32_t flag[kFcWindow];
+            Acc val[kFcWindow];
+#pragma unroll
+            for (int j = 0; j < kFcWindow; ++j) {
+                const int64_t mine = look - 32 * j - lane;
+                val[j] = scan_identity<Acc, OP>();
+                flag[j] = mine >= 0 ? state.peek(base + mine, val[j]) : (uint32_t)FLAG_PREFIX;
+            }
+#pragma unroll
+            for (int j = 0; j < kFcWindow; ++j) {
+                if (done || failed) continue;
+                const int64_t mine = look - 32 * j - lane;
+                bool abort = false;
+                uint32_t polls = 0;
+                while (flag[j] == FLAG_EMPTY) {
+                    ++polls;
+                    if (polls > pl.max_polls) { abort = true; break; }
+                    if ((polls & 1023u) == 0 && error_latched(err_word)) { abort = true; break; }
+                    if (polls > 32) __nanosleep(polls > 256 ? 256 : 32);      // the first reads just spin: neighbours publish within a microsecond
+                    flag[j] = state.peek(base + mine, val[j]);
+                }
+                if (__any_sync(0xffffffffu, abort)) { failed = true; continue; }
+                const uint32_t pmask = __ballot_sync(0xffffffffu, flag[j] == FLAG_PREFIX);
+                const int stop = pmask ? (__ffs(pmask) - 1) : 32;
+                Acc contrib = (lane <= stop && mine >= 0) ? val[j] : scan_identity<Acc, OP>();
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const Acc up = __shfl_down_sync(0xffffffffu, contrib, o);
+                    if (lane + o < 32) contrib = scan_apply<Acc, OP>(up, contrib);
+                }
+                running = running_set ? scan_apply<Acc, OP>(contrib, running) : contrib;     // valid in lane 0
+                running_set = true;
+                if (stop < 32) done = true;
+            }
+            look -= 32 * kFcWindow;
+        }
+        if (lane == 0) {
+            if (failed) {
+                s_abort = 1;
+            } else {
+                s_prefix[warp] = running;
+                state.publish(base + tt, FLAG_PREFIX, scan_apply<Acc, OP>(running, s_coltot[warp]));
+            }
+        }
+    }
+    __syncthreads();
+    if (s_abort) {
+        if (tid == 0) latch_error(err_word, B200_LOOKBACK_TIMEOUT);
+        return;
+    }
+    // offsets, outputs, stores
+    const bool seeded = tt > 0 || pl.has_init;
+    Acc off[KC];
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+        Acc before = scan_identity<Acc, OP>();
+        for (int w = 0; w < warp; ++w) before = scan_apply<Acc, OP>(before, s_wtot[w][k]);
+        Acc o = scan_apply<Acc, OP>(before, wex[k]);
+        if (seeded) o = scan_apply<Acc, OP>(s_prefix[k], o);
+        off[k] = o;
+    }
+    T out[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        if (pl.inclusive) out[e] = scan_down<T>(scan_apply<Acc, OP>(off[e % KC], x[e]));
+        else out[e] = scan_down<T>(e < KC ? off[e % KC] : scan_apply<Acc, OP>(off[e % KC], x[e - KC]));
+    }
+    if (full && pl.vec_ok) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            VT v;
+#pragma unroll
+            for (int q = 0; q < VE; ++q) v.v[q] = out[j * VE + q];
+            __stcs(reinterpret_cast<uint4*>(dst) + j, __builtin_bit_cast(uint4, v));
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) if (row0 + e / KC < pl.L) dst[e] = out[e];
+    }
+}
+
+template <typename T, int OP, int KC>
+static int32_t launch_scan_fewcols(b200_stream_t st, const void* A, void* B, ScanPlan pl, bool aligned) {
+    using Acc = typename ScanAcc<T>::type;
+    constexpr int ROWS = kFcThreads * fc_rows_per_thread(sizeof(T));
+    pl.tiles_per_col = (pl.L + ROWS - 1) / ROWS;
+    pl.ntiles = pl.tiles_per_col * pl.M;
+    if (pl.ntiles * KC >= (int64_t)1 << 31) return fail(B200_TOO_LARGE, "accumulate: too many tiles");
+    // every tile start is 16-byte aligned when the slabs are
+    pl.vec_ok = (aligned && (pl.M == 1 || (pl.K * pl.L * (int64_t)sizeof(T)) % 16 == 0)) ? 1 : 0;
+    void* flags = nullptr;
+    B200_TRY(descriptor_storage<Acc>(st, pl.ntiles * KC, &flags, &pl.value_mem, &pl.epoch));
+    void* unused = nullptr;
+    unsigned int* counters = nullptr;
+    B200_TRY(scratch(st, 0, &unused, &counters));
+    unsigned int* ticket = counters + (kCounterBytes / sizeof(unsigned int) - 1);
+    scan_fewcols_kernel<T, OP, KC><<<(unsigned)pl.ntiles, kFcThreads, 0, st->s>>>((const T*)A, (T*)B, pl, flags, ticket,
+                                                                                  device_error_word(st->dev));
+    return B200_OK;
+}
+
 // One thread per column: sequential walk, coalesced across neighbouring columns when K > 1.
 template <typename T, int OP>
 __global__ void __launch_bounds__(256)
@@ -833,6 +1036,15 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         constexpr int V = 16 / sizeof(T);
         if (aligned && (pl.K * sizeof(T)) % 16 == 0) return launch_scan_strided<T, OP, V>(st, A, B, pl);
         return launch_scan_strided<T, OP, 1>(st, A, B, pl);
+    }
+    // a few long interleaved columns: one tile holds all of them (8-byte elements measured no
+    // faster than the per-column tiles: their tiles are half as long, the chain twice as long)
+    if constexpr (sizeof(T) <= 4) if (pl.K >= 2 && pl.K <= 4 && pl.L >= 4096) {
+        switch (pl.K) {
+            case 2: return launch_scan_fewcols<T, OP, 2>(st, A, B, pl, aligned);
+            case 3: return launch_scan_fewcols<T, OP, 3>(st, A, B, pl, aligned);
+            default: return launch_scan_fewcols<T, OP, 4>(st, A, B, pl, aligned);
+        }
     }
     const bool thread_cols = (pl.L <= 32 && ncols >= 1024) || (pl.K > 1 && ncols >= 4096);
     if (thread_cols) {

@@ -156,6 +156,54 @@ def test_scans_down_a_strided_dimension(gpu, orc, sizes):
     assert_close(dst.to_host(), orc.accumulate("+", src.to_host(), axis=1), 1e-5)
 
 
+@pytest.mark.parametrize("sizes", [(3, 1_000_000), (2, 4096), (4, 4097), (3, 100_003), (2, 70_000, 3), (3, 5000, 4), (4, 300_001)])
+def test_scans_down_a_few_long_columns(gpu, orc, sizes):
+    """accumulate(op, A; dims=2) with two to four interleaved columns (the reference benchmarks
+    3 x 1 000 000): the kernel whose tiles hold all columns of a row range.  Every element size,
+    all operators, seeded and exclusive forms, several slabs, a ragged last tile, in place, and an
+    operand that starts off a 16-byte boundary."""
+    rng = np.random.default_rng(6)
+    for dt in (np.float32, np.float64, np.int32, np.int64, np.float16):
+        dt = np.dtype(dt)
+        if dt.kind == "i":
+            x = rng.integers(-3, 4, sizes).astype(dt)
+        elif dt.itemsize == 2:
+            x = np.where(rng.random(sizes) < 0.5, 1.0, -1.0).astype(dt)      # partial sums stay small and exact
+        else:
+            x = (rng.random(sizes) - 0.25).astype(dt)
+        xd = gpu.ROCArray.from_host(x)
+        for op in ("+", "max", "min"):
+            got = gpu.accumulate(op, xd, dims=2, init=None).to_host()
+            ref = orc.accumulate(op, x, axis=1)
+            if dt.kind == "i" or op in ("max", "min"):
+                assert np.array_equal(got.astype(np.float64), np.asarray(ref, dtype=np.float64)), (sizes, dt, op)
+            else:
+                wide = np.cumsum(x.astype(np.float64), axis=1)
+                tol = 5e-2 if dt.itemsize == 2 else (1e-4 if dt.itemsize == 4 else 1e-11)
+                assert np.all(np.abs(got.astype(np.float64) - wide) <= tol * np.maximum(np.abs(wide), 1.0)), (sizes, dt, op)
+        if dt.kind == "i":
+            seed = dt.type(5)
+            assert np.array_equal(gpu.accumulate("+", xd, dims=2, init=seed).to_host(), orc.accumulate("+", x, axis=1, init=seed)), (sizes, dt)
+            out = gpu.ROCArray(dt, sizes)
+            gpu.accumulate_("+", out, xd, dims=2, init=dt.type(-2), inclusive=False)
+            incl = np.cumsum(x, axis=1, dtype=dt)
+            excl = np.concatenate([np.zeros_like(incl[:, :1]), incl[:, :-1]], axis=1) - dt.type(2)
+            assert np.array_equal(out.to_host(), excl), (sizes, dt)
+            assert gpu.accumulate_("+", xd, xd, dims=2, init=None) is xd             # in place
+            assert np.array_equal(xd.to_host(), incl), (sizes, dt)
+    if len(sizes) == 2:
+        # factors spread over a binade (no rounding ties): products of a million Float32 factors
+        f = np.exp(rng.uniform(-1e-3, 1e-3, sizes)).astype(np.float32)
+        got = gpu.accumulate("*", gpu.ROCArray.from_host(f), dims=2, init=None).to_host()
+        assert_close(got, np.cumprod(f.astype(np.float64), axis=1), 1e-3, (sizes, "prod"))
+        # an operand one element past a 16-byte boundary: element-wise accesses, same tiles
+        n = sizes[0] * sizes[1]
+        big = gpu.ROCArray.from_host(rng.integers(-3, 4, n + 1).astype(np.int32))
+        src = big.view(1, n + 1).reshape(sizes)
+        want = np.cumsum(big.to_host()[1:].reshape(sizes, order="F"), axis=1, dtype=np.int32)
+        assert np.array_equal(gpu.accumulate("+", src, dims=2, init=None).to_host(), want), sizes
+
+
 def test_long_vector_scan_forms(gpu, orc):
     """The persistent kernel for long dense vectors: in place, exclusive, seeded, max/min/prod, 16-bit
     elements, a last segment of every fill level, many launches in a row (descriptor words tagged
