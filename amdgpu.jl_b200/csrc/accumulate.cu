@@ -466,17 +466,20 @@ scan_segment_kernel(const T* A, T* B, SegPlan pl, void* state_mem, int32_t* err_
         for (int q = 0; q < V; ++q) acc[q] = scan_identity<Acc, OP>();
         const int64_t v0 = seg * pl.seg_vecs;
         const int64_t v1 = (v0 + pl.seg_vecs < pl.nvec) ? v0 + pl.seg_vecs : pl.nvec;
-        for (int64_t base = v0; base < v1; base += kSubTileVecs) {
-            VT v[kScanVecs];
-            bool on[kScanVecs];
+        // two sub-tiles per step: eight loads in flight per thread (nothing else keeps the memory
+        // pipes busy during the prologue)
+        constexpr int NL = 2 * kScanVecs;
+        for (int64_t base = v0; base < v1; base += 2 * kSubTileVecs) {
+            VT v[NL];
+            bool on[NL];
 #pragma unroll
-            for (int j = 0; j < kScanVecs; ++j) {
+            for (int j = 0; j < NL; ++j) {
                 const int64_t vi = base + j * kSegThreads + tid;
                 on[j] = vi < v1;
                 if (on[j]) v[j] = __builtin_bit_cast(VT, ld_policy16(src + vi, keep));
             }
 #pragma unroll
-            for (int j = 0; j < kScanVecs; ++j)
+            for (int j = 0; j < NL; ++j)
                 if (on[j]) {
 #pragma unroll
                     for (int q = 0; q < V; ++q) acc[q] = scan_apply<Acc, OP>(acc[q], scan_up<T>(v[j].v[q]));
