@@ -3,7 +3,7 @@
 // Every rank owns a few hundred bytes of slots that all ranks of the group can write.  The
 // reduction kernel's last block stores its partial straight into every rank's slots and reads the
 // partials of the others from its own buffer - no separate collective launch, no host round trip.
-// Plain stores and loads only (system-scope fences, no multicast, no library kernel on peer memory).
+// Plain one-to-one stores and loads only (system-scope fences, no library kernel on peer memory).
 //
 // Three transports place the slots differently; the kernel code is the same for all:
 //   * B200_PEER_HOST: the slots live in POSIX shared memory that every rank registers with the
