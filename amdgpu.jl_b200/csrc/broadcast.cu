@@ -642,8 +642,10 @@ static void operand_span(const b200_tensor& t, const PermutePlan& pl, uintptr_t*
 
 // `fixed` receives the leaves to use: permuted operands replaced by dense copies in the stream's
 // scratch.  Without room for the copies the leaves stay as they are (the strided path works).
+// With `pool_temp` the copies live in one stream-ordered pool allocation that the caller frees on the
+// stream after its launches (for operators that use the stream's scratch themselves).
 int32_t densify_permuted_leaves(b200_stream_t st, const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
-                                int32_t nleaves, b200_leaf* fixed) {
+                                int32_t nleaves, b200_leaf* fixed, void** pool_temp) {
     size_t total = 0;
     PermutePlan plan[B200_MAX_LEAVES];
     bool take[B200_MAX_LEAVES];
@@ -657,7 +659,12 @@ int32_t densify_permuted_leaves(b200_stream_t st, const int64_t* shape, int32_t 
     }
     if (total == 0) return B200_OK;
     void* scr = nullptr;
-    if (scratch(st, total, &scr) != B200_OK) return B200_OK;
+    if (pool_temp) {
+        if (b200_malloc_async(&scr, total, st) != B200_OK) return B200_OK;
+        *pool_temp = scr;
+    } else if (scratch(st, total, &scr) != B200_OK) {
+        return B200_OK;
+    }
     unsigned char* p = reinterpret_cast<unsigned char*>(scr);
     for (int k = 0; k < nleaves; ++k) {
         if (!take[k]) continue;
@@ -719,7 +726,7 @@ extern "C" int32_t b200_broadcast(b200_stream_t st, const b200_tensor* out, cons
             }
         }
         b200_leaf fixed[B200_MAX_LEAVES];
-        B200_TRY(densify_permuted_leaves(st, out->shape, out->ndim, leaves, nleaves, fixed));
+        B200_TRY(densify_permuted_leaves(st, out->shape, out->ndim, leaves, nleaves, fixed, nullptr));
         B200_TRY(compile_program(out->shape, out->ndim, fixed, nleaves, program, ninstr, out->dtype, &C));
     }
     for (int d = 0; d < out->ndim; ++d)

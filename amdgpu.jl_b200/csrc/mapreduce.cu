@@ -697,6 +697,18 @@ static int32_t mapreduce_impl(b200_stream_t st, const b200_tensor* R, const int6
     }
     Compiled C;
     B200_TRY(compile_program(shape, ndim, leaves, nleaves, program, ninstr, acc_dt, &C));
+    // operands that are transposed / permuted views: dense copies first (one pool allocation, freed
+    // on the stream when this call has enqueued its kernels)
+    struct PoolTemp {
+        b200_stream_t st;
+        void* ptr = nullptr;
+        ~PoolTemp() { if (ptr) b200_free_async(ptr, st); }
+    } temp{st};
+    b200_leaf fixed[B200_MAX_LEAVES];
+    if (!prepare_only && !C.P.linear && n > 0 && leaves && nleaves > 0 && nleaves <= B200_MAX_LEAVES) {
+        B200_TRY(densify_permuted_leaves(st, shape, ndim, leaves, nleaves, fixed, &temp.ptr));
+        if (temp.ptr) B200_TRY(compile_program(shape, ndim, fixed, nleaves, program, ninstr, acc_dt, &C));
+    }
 
     // ---- fast paths: one dense array, f in {identity, abs, abs2}
     const ProgramDesc& P = C.P;

@@ -83,6 +83,9 @@ int32_t compile_program(const int64_t* shape, int32_t ndim, const b200_leaf* lea
 // inside a stream capture (-1); compile it without launching.
 int jit_broadcast(b200_stream_t st, const Compiled& C, const LeafDesc& O, int64_t n);
 int32_t jit_prepare_reduce(const Compiled& C, int out_dtype, int redop, int acc_dtype, int full);
+// Replaces operands that are transposed / permuted views by dense copies (broadcast.cu).
+int32_t densify_permuted_leaves(b200_stream_t st, const int64_t* shape, int32_t ndim, const b200_leaf* leaves,
+                                int32_t nleaves, b200_leaf* fixed, void** pool_temp);
 int32_t jit_prepare(const Compiled& C, int out_dtype);
 int jit_reduce_kernel(b200_stream_t st, const Compiled& C, int out_dtype, int redop, int acc_dtype, int full,
                       const void** kernel, int64_t* resident);

@@ -202,3 +202,33 @@ def test_permuted_operands_of_higher_rank(gpu):
     # short first dimension: stays on the strided path and must still be right
     S = fa(rng, (3000, 5))
     assert bits_equal(gpu.ROCArray.from_host(S).transpose().copy().to_host(), np.asfortranarray(S.T))
+
+
+def test_reductions_over_permuted_operands(gpu, orc):
+    """mapreduce whose operand is a large transposed / permuted view: the view is copied into dense
+    form first (a pool temporary that is freed on the stream), then the ordinary kernels run."""
+    rng = np.random.default_rng(15)
+
+    def fp(shape):                                   # positive data: the sums are well conditioned
+        return np.asfortranarray(rng.random(shape).astype(np.float32))
+    K = fp((300, 200))
+    Kd = gpu.ROCArray.from_host(K)
+    gpu.synchronize()
+    live = gpu.pool_stats()["live_bytes"]
+    T = Kd.transpose()                                            # 200 x 300
+    assert_close(gpu.sum(T, dims=1).to_host(), K.T.astype(np.float64).sum(axis=0, keepdims=True), 1e-5)
+    assert_close(gpu.sum(T, dims=2).to_host(), K.T.astype(np.float64).sum(axis=1, keepdims=True), 1e-5)
+    assert bits_equal(gpu.maximum(T, dims=2).to_host(), K.T.max(axis=1, keepdims=True))
+    assert_close(gpu.sum(T), K.astype(np.float64).sum(), 1e-5)
+    H = fp((200, 300))
+    Hd = gpu.ROCArray.from_host(H)
+    got = gpu.mapreduce(None, "+", Hd.dot * T.dot)
+    assert_close(got, (H.astype(np.float64) * K.T).sum(), 1e-5)
+    got = gpu.mapreduce(None, "max", gpu.broadcast.abs_(Hd.dot - T.dot), dims=1).to_host()
+    assert bits_equal(got, np.abs(H - K.T).max(axis=0, keepdims=True))
+    P3 = fp((30, 40, 50))
+    Pd = gpu.ROCArray.from_host(P3).permuteddims((3, 1, 2))      # 50 x 30 x 40
+    ref = P3.transpose(2, 0, 1).astype(np.float64)
+    assert_close(gpu.sum(Pd, dims=(1, 3)).to_host(), ref.sum(axis=(0, 2), keepdims=True), 1e-5)
+    gpu.synchronize()
+    assert gpu.pool_stats()["live_bytes"] == live + Hd.nbytes + P3.nbytes      # the temporaries are gone
