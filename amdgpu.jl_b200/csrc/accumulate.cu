@@ -1027,6 +1027,91 @@ scan_column_thread_kernel(const T* A, T* B, ScanPlan pl) {
     }
 }
 
+// One warp per contiguous column (K == 1): cumsum(A; dims=1) of a 512 x 1000 matrix and the like -
+// many columns, each a few hundred to a few thousand elements.  A lane takes a 16-byte vector per
+// step (scalar elements when the columns are not 16-byte aligned), the warp scans the vector totals
+// with shuffles and carries the running value down the column; the loads of four steps are in
+// flight together.  No descriptors, no tickets, no waiting on other blocks: the tiled kernels
+// spend a whole 256-thread tile and a look-back on such a column.
+template <typename T, int OP, bool VEC>
+__global__ void __launch_bounds__(256)
+scan_column_warp_kernel(const T* A, T* B, ScanPlan pl) {
+    using Acc = typename ScanAcc<T>::type;
+    constexpr int V = VEC ? 16 / (int)sizeof(T) : 1;
+    constexpr int U = 4;
+    using VT = Vec<T, V>;
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const int64_t steps = (pl.L + 32 * V - 1) / (32 * V);
+    for (int64_t col = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); col < pl.M; col += nwarps) {
+        const T* src = A + col * pl.L;
+        T* dst = B + col * pl.L;
+        Acc carry = pl.has_init ? scan_seed<T>(pl) : scan_identity<Acc, OP>();
+        bool seeded = pl.has_init != 0;
+        for (int64_t s0 = 0; s0 < steps; s0 += U) {
+            Acc x[U][V];
+            bool on[U][V];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t e0 = ((s0 + u) * 32 + lane) * V;
+                bool whole = false;
+                if constexpr (VEC) {
+                    whole = e0 + V <= pl.L;
+                    if (whole) {
+                        const VT v = __builtin_bit_cast(VT, __ldcs(reinterpret_cast<const uint4*>(src + e0)));
+#pragma unroll
+                        for (int q = 0; q < V; ++q) { x[u][q] = scan_up<T>(v.v[q]); on[u][q] = true; }
+                    }
+                }
+                if (!whole) {
+#pragma unroll
+                    for (int q = 0; q < V; ++q) {
+                        on[u][q] = e0 + q < pl.L;
+                        x[u][q] = on[u][q] ? scan_up<T>(src[e0 + q]) : scan_identity<Acc, OP>();
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (s0 + u >= steps) continue;                   // uniform over the warp
+#pragma unroll
+                for (int q = 1; q < V; ++q) x[u][q] = scan_apply<Acc, OP>(x[u][q - 1], x[u][q]);
+                const Acc inc = warp_scan_inclusive<Acc, OP>(x[u][V - 1], lane);
+                Acc before = __shfl_up_sync(0xffffffffu, inc, 1);           // total of the lanes in front
+                const Acc total = __shfl_sync(0xffffffffu, inc, 31);
+                Acc off = carry;
+                bool off_set = seeded;
+                if (lane > 0) { off = off_set ? scan_apply<Acc, OP>(carry, before) : before; off_set = true; }
+                const int64_t e0 = ((s0 + u) * 32 + lane) * V;
+                T outv[V];
+#pragma unroll
+                for (int q = 0; q < V; ++q) {
+                    const Acc incl = off_set ? scan_apply<Acc, OP>(off, x[u][q]) : x[u][q];
+                    const Acc excl = q == 0 ? (off_set ? off : scan_identity<Acc, OP>())
+                                            : (off_set ? scan_apply<Acc, OP>(off, x[u][q - 1]) : x[u][q - 1]);
+                    outv[q] = scan_down<T>(pl.inclusive ? incl : excl);
+                }
+                bool whole = false;
+                if constexpr (VEC) {
+                    whole = e0 + V <= pl.L;
+                    if (whole) {
+                        VT v;
+#pragma unroll
+                        for (int q = 0; q < V; ++q) v.v[q] = outv[q];
+                        __stcs(reinterpret_cast<uint4*>(dst + e0), __builtin_bit_cast(uint4, v));
+                    }
+                }
+                if (!whole) {
+#pragma unroll
+                    for (int q = 0; q < V; ++q) if (on[u][q]) dst[e0 + q] = outv[q];
+                }
+                carry = seeded ? scan_apply<Acc, OP>(carry, total) : total;
+                seeded = true;
+            }
+        }
+    }
+}
+
 template <typename T, int OP>
 static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl) {
     using Acc = typename ScanAcc<T>::type;
@@ -1054,6 +1139,16 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         int64_t blocks = (ncols + 255) / 256;
         if (blocks > target) blocks = target;
         scan_column_thread_kernel<T, OP><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
+        return B200_OK;
+    }
+    // many contiguous columns of moderate length: a warp per column
+    if (pl.K == 1 && pl.M >= 64 && pl.L > 32 && pl.L * (int64_t)sizeof(T) <= 32768) {
+        int64_t blocks = (pl.M + 7) / 8;
+        if (blocks > target) blocks = target;
+        if (aligned && (pl.L * sizeof(T)) % 16 == 0)
+            scan_column_warp_kernel<T, OP, true><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
+        else
+            scan_column_warp_kernel<T, OP, false><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
         return B200_OK;
     }
     if (ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {

@@ -204,6 +204,39 @@ def test_scans_down_a_few_long_columns(gpu, orc, sizes):
         assert np.array_equal(gpu.accumulate("+", src, dims=2, init=None).to_host(), want), sizes
 
 
+@pytest.mark.parametrize("sizes", [(512, 1000), (100, 70), (33, 64), (8192, 64), (4100, 65), (36, 10, 20)])
+def test_scans_down_many_contiguous_columns(gpu, orc, sizes):
+    """accumulate(op, A; dims=1) with at least 64 columns of 33 to 8192 elements (the reference
+    benchmarks 512 x 1000): one warp per column.  Vector and element-wise accesses, ragged last
+    steps, all operators, seeded, exclusive and in-place forms."""
+    rng = np.random.default_rng(8)
+    for dt in (np.float32, np.int64, np.float16, np.int32):
+        dt = np.dtype(dt)
+        x = rng.integers(-3, 4, sizes).astype(dt) if dt.kind == "i" else (rng.random(sizes) - 0.25).astype(dt)
+        xd = gpu.ROCArray.from_host(x)
+        for op in ("+", "max", "min"):
+            got = gpu.accumulate(op, xd, dims=1, init=None).to_host()
+            ref = orc.accumulate(op, x, axis=0)
+            if dt.kind == "i" or op in ("max", "min"):
+                assert np.array_equal(got.astype(np.float64), np.asarray(ref, dtype=np.float64)), (sizes, dt, op)
+            else:
+                wide = np.cumsum(x.astype(np.float64), axis=0)
+                tol = 2e-2 if dt.itemsize == 2 else 1e-5
+                assert np.all(np.abs(got.astype(np.float64) - wide) <= tol * np.maximum(np.abs(wide), 1.0)), (sizes, dt, op)
+        if dt.kind == "i":
+            seed = dt.type(7)
+            assert np.array_equal(gpu.accumulate("+", xd, dims=1, init=seed).to_host(), orc.accumulate("+", x, axis=0, init=seed)), (sizes, dt)
+            out = gpu.ROCArray(dt, sizes)
+            gpu.accumulate_("+", out, xd, dims=1, init=dt.type(3), inclusive=False)
+            incl = np.cumsum(x, axis=0, dtype=dt)
+            excl = np.concatenate([np.zeros_like(incl[:1]), incl[:-1]], axis=0) + dt.type(3)
+            assert np.array_equal(out.to_host(), excl), (sizes, dt)
+            assert gpu.accumulate_("+", xd, xd, dims=1, init=None) is xd
+            assert np.array_equal(xd.to_host(), incl), (sizes, dt)
+    f = np.exp(rng.uniform(-1e-2, 1e-2, sizes)).astype(np.float32)
+    assert_close(gpu.accumulate("*", gpu.ROCArray.from_host(f), dims=1, init=None).to_host(), np.cumprod(f.astype(np.float64), axis=0), 1e-4, (sizes, "prod"))
+
+
 def test_long_vector_scan_forms(gpu, orc):
     """The persistent kernel for long dense vectors: in place, exclusive, seeded, max/min/prod, 16-bit
     elements, a last segment of every fill level, many launches in a row (descriptor words tagged
