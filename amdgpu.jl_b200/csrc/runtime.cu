@@ -135,6 +135,34 @@ int32_t enter(b200_stream_t st) {
 int32_t* device_error_word(int dev) { return g_dev[dev]->err_dev; }
 int sm_count(int dev) { return g_dev[dev]->sms; }
 
+int cached_blocks_per_sm(const void* kernel, int threads, size_t dyn_smem, int dev) {
+    struct Key {
+        const void* k; int threads; size_t smem; int dev;
+        bool operator==(const Key& o) const { return k == o.k && threads == o.threads && smem == o.smem && dev == o.dev; }
+    };
+    struct Hash {
+        size_t operator()(const Key& x) const {
+            return std::hash<const void*>()(x.k) ^ (std::hash<size_t>()(x.smem) * 31) ^ ((size_t)x.threads << 20) ^ ((size_t)x.dev << 40);
+        }
+    };
+    static std::mutex mu;
+    static std::unordered_map<Key, int, Hash> cache;
+    const Key key{kernel, threads, dyn_smem, dev};
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) return it->second;
+    }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dyn_smem) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        per_sm = 1;
+    }
+    std::lock_guard<std::mutex> lk(mu);
+    cache[key] = per_sm;
+    return per_sm;
+}
+
 int32_t finish(b200_stream_t st, const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, what);
