@@ -155,3 +155,43 @@ def test_missing_rank_times_out_and_group_recovers(gpu, tmp_path):
     port = 33600 + (os.getpid() % 2000)
     mp.spawn(_skipped_step_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def test_arrays_on_two_devices_of_one_process(gpu):
+    """One process, two devices, switched with ``device!`` (test/hip_rocarray/multi_gpu.jl:30-93):
+    arrays stay on the device they were made on, reductions and broadcasts run on the current
+    device, data moves between the devices through the host."""
+    if gpu.ndevices() < 2:
+        pytest.skip("needs two GPUs")
+    try:
+        gpu.device_(0)
+        x1 = gpu.ones(np.int64, 16)
+        assert x1.device == 0
+        gpu.device_(1)
+        x2 = gpu.ones(np.int64, 16)
+        assert x2.device == 1 and gpu.current_device() == 1
+        assert gpu.sum(x2) == 16
+        gpu.device_(0)
+        assert gpu.sum(x1) == 16
+        # copyto! through a host array (multi_gpu.jl:52-68)
+        h = np.arange(16, dtype=np.int32) * 3 - 7
+        a = gpu.ROCArray.from_host(h)
+        host = a.to_host()
+        gpu.device_(1)
+        b = gpu.zeros(np.int32, 16)
+        b.copy_from_host(host)
+        assert np.array_equal(b.to_host(), h)
+        # the same operator on each device in turn (multi_gpu.jl:70-93, x .+= 1 in place of the kernel)
+        gpu.device_(0)
+        y1 = gpu.zeros(np.int32, 1 << 20)
+        gpu.materialize_(y1, y1.dot + np.int32(1))
+        gpu.device_(1)
+        y2 = gpu.zeros(np.int32, 1 << 20)
+        gpu.materialize_(y2, y2.dot + np.int32(1))
+        assert gpu.sum(y2) == 1 << 20
+        assert int(gpu.cumsum(y2).to_host()[-1]) == 1 << 20
+        gpu.device_(0)
+        assert gpu.sum(y1) == 1 << 20
+        gpu.synchronize()
+    finally:
+        gpu.device_(0)
