@@ -121,6 +121,7 @@ static int32_t descriptor_storage(b200_stream_t st, int64_t ntiles, void** flag_
 template <typename T, int OP>
 __global__ void __launch_bounds__(kScanThreads)
 scan_lookback_kernel(const T* A, T* B, ScanPlan pl, void* state_mem, unsigned int* ticket, int32_t* err_word) {
+    grid_dependency_wait();
     using Acc = typename ScanAcc<T>::type;
     constexpr int V = 16 / sizeof(T);
     constexpr int TILE = kScanThreads * kScanVecs * V;
@@ -632,6 +633,7 @@ template <typename T, int OP, int VEC>
 __global__ void __launch_bounds__(256)
 scan_strided_kernel(const T* A, T* B, StridedScanPlan pl, unsigned long long* flags, typename ScanAcc<T>::type* agg,
                     typename ScanAcc<T>::type* pre, unsigned int* ticket, int32_t* err_word) {
+    grid_dependency_wait();
     using Acc = typename ScanAcc<T>::type;
     using VT = Vec<T, VEC>;
     constexpr int KX = 32 * VEC;                    // columns per strip
@@ -796,9 +798,9 @@ static int32_t launch_scan_strided(b200_stream_t st, const void* A, void* B, con
     B200_TRY(scratch(st, 2 * vbytes, &scr, &counters));
     unsigned char* base = reinterpret_cast<unsigned char*>(scr);
     unsigned int* ticket = counters + (kCounterBytes / sizeof(unsigned int) - 1);
-    scan_strided_kernel<T, OP, VEC><<<(unsigned)sp.ntiles, 256, 0, st->s>>>(
-        (const T*)A, (T*)B, sp, flags, reinterpret_cast<Acc*>(base),
-        reinterpret_cast<Acc*>(base + vbytes), ticket, device_error_word(st->dev));
+    launch_overlapped(scan_strided_kernel<T, OP, VEC>, (unsigned)sp.ntiles, 256, 0, st->s,
+                      (const T*)A, (T*)B, sp, flags, reinterpret_cast<Acc*>(base),
+                      reinterpret_cast<Acc*>(base + vbytes), ticket, device_error_word(st->dev));
     return B200_OK;
 }
 
@@ -820,6 +822,7 @@ __host__ __device__ constexpr int fc_rows_per_thread(size_t elem) { return elem 
 template <typename T, int OP, int KC>
 __global__ void __launch_bounds__(kFcThreads)
 scan_fewcols_kernel(const T* A, T* B, ScanPlan pl, void* flag_mem, unsigned int* ticket, int32_t* err_word) {
+    grid_dependency_wait();
     using Acc = typename ScanAcc<T>::type;
     constexpr int RPT = fc_rows_per_thread(sizeof(T));   // rows per thread
     constexpr int E = RPT * KC;                      // elements per thread, element e = row e / KC, column e % KC
@@ -1000,8 +1003,8 @@ static int32_t launch_scan_fewcols(b200_stream_t st, const void* A, void* B, Sca
     unsigned int* counters = nullptr;
     B200_TRY(scratch(st, 0, &unused, &counters));
     unsigned int* ticket = counters + (kCounterBytes / sizeof(unsigned int) - 1);
-    scan_fewcols_kernel<T, OP, KC><<<(unsigned)pl.ntiles, kFcThreads, 0, st->s>>>((const T*)A, (T*)B, pl, flags, ticket,
-                                                                                  device_error_word(st->dev));
+    launch_overlapped(scan_fewcols_kernel<T, OP, KC>, (unsigned)pl.ntiles, kFcThreads, 0, st->s, (const T*)A, (T*)B, pl, flags, ticket,
+                      device_error_word(st->dev));
     return B200_OK;
 }
 
@@ -1009,6 +1012,7 @@ static int32_t launch_scan_fewcols(b200_stream_t st, const void* A, void* B, Sca
 template <typename T, int OP>
 __global__ void __launch_bounds__(256)
 scan_column_thread_kernel(const T* A, T* B, ScanPlan pl) {
+    grid_dependency_wait();
     using Acc = typename ScanAcc<T>::type;
     const int64_t ncols = pl.K * pl.M;
     const int64_t nthr = (int64_t)gridDim.x * blockDim.x;
@@ -1036,6 +1040,7 @@ scan_column_thread_kernel(const T* A, T* B, ScanPlan pl) {
 template <typename T, int OP, bool VEC>
 __global__ void __launch_bounds__(256)
 scan_column_warp_kernel(const T* A, T* B, ScanPlan pl) {
+    grid_dependency_wait();
     using Acc = typename ScanAcc<T>::type;
     constexpr int V = VEC ? 16 / (int)sizeof(T) : 1;
     constexpr int U = 4;
@@ -1146,9 +1151,9 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
         int64_t blocks = (pl.M + 7) / 8;
         if (blocks > target) blocks = target;
         if (aligned && (pl.L * sizeof(T)) % 16 == 0)
-            scan_column_warp_kernel<T, OP, true><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
+            launch_overlapped(scan_column_warp_kernel<T, OP, true>, (unsigned)blocks, 256, 0, st->s, (const T*)A, (T*)B, pl);
         else
-            scan_column_warp_kernel<T, OP, false><<<(unsigned)blocks, 256, 0, st->s>>>((const T*)A, (T*)B, pl);
+            launch_overlapped(scan_column_warp_kernel<T, OP, false>, (unsigned)blocks, 256, 0, st->s, (const T*)A, (T*)B, pl);
         return B200_OK;
     }
     if (ncols == 1 && aligned && (pl.L * sizeof(T)) % 16 == 0 && pl.L * (int64_t)sizeof(T) >= (int64_t)(1 << 20)) {
@@ -1187,8 +1192,8 @@ static int32_t launch_scan(b200_stream_t st, const void* A, void* B, ScanPlan pl
     B200_TRY(scratch(st, 0, &unused, &counters));
     // the last counter slot serves as the tile ticket (it returns to zero by itself)
     unsigned int* ticket = counters + (kCounterBytes / sizeof(unsigned int) - 1);
-    scan_lookback_kernel<T, OP><<<(unsigned)pl.ntiles, kScanThreads, 0, st->s>>>(
-        (const T*)A, (T*)B, pl, scr, ticket, device_error_word(st->dev));
+    launch_overlapped(scan_lookback_kernel<T, OP>, (unsigned)pl.ntiles, kScanThreads, 0, st->s,
+                      (const T*)A, (T*)B, pl, scr, ticket, device_error_word(st->dev));
     return B200_OK;
 }
 
