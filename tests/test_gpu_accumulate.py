@@ -204,10 +204,10 @@ def test_scans_down_a_few_long_columns(gpu, orc, sizes):
         assert np.array_equal(gpu.accumulate("+", src, dims=2, init=None).to_host(), want), sizes
 
 
-@pytest.mark.parametrize("sizes", [(512, 1000), (100, 70), (33, 64), (8192, 64), (4100, 65), (36, 10, 20)])
+@pytest.mark.parametrize("sizes", [(512, 1000), (100, 70), (33, 64), (2048, 64), (1030, 65), (8192, 64), (36, 10, 20)])
 def test_scans_down_many_contiguous_columns(gpu, orc, sizes):
-    """accumulate(op, A; dims=1) with at least 64 columns of 33 to 8192 elements (the reference
-    benchmarks 512 x 1000): one warp per column.  Vector and element-wise accesses, ragged last
+    """accumulate(op, A; dims=1) with at least 64 columns of 33 elements to 8 KiB (the reference
+    benchmarks 512 x 1000): one warp per column; longer columns take the tiled kernel.  Vector and element-wise accesses, ragged last
     steps, all operators, seeded, exclusive and in-place forms."""
     rng = np.random.default_rng(8)
     for dt in (np.float32, np.int64, np.float16, np.int32):
